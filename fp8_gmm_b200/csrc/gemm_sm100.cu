@@ -1,0 +1,723 @@
+// Grouped FP8 GEMM for B200 (sm_100a): persistent, warp-specialised tcgen05 / TMEM kernel.
+//
+// Replaces the reference's CUTLASS Sm90 grouped GEMM (csrc/fp8_gmm.cu:46-80,82-161), its separate
+// de-scale pass (csrc/multi_pointwise.cu:99-151) and the per-group cuBLASLt loops (fp8_gmm/backend.py:
+// 84-96; wgrad: fp8_gmm/grouped_linear.py:165-182) with one launch per GEMM.
+//
+// Kernel shape
+//   * one persistent CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM
+//     owner), warps 2-5 = epilogue (each owns the 32 TMEM lanes its warp id selects);
+//   * output tile 128 x 256, K step 128 bytes (one 128-byte swizzle atom), 4-stage shared-memory ring
+//     (48 KiB per stage: A 128x128 B + B 256x128 B, both K-major, written by TMA with SWIZZLE_128B);
+//   * tcgen05.mma.cta_group::1.kind::f8f6f4, M=128 N=256 K=32, fp32 accumulators in TMEM; the 512 TMEM
+//     columns hold two accumulators so the epilogue of tile i overlaps the main loop of tile i+1;
+//   * epilogue: tcgen05.ld -> (a_scale_inv*b_scale_inv) -> bf16 -> predicated 16-byte stores (a tile may
+//     straddle the end of its group, so rows are masked); optional fused activation (GELU or SwiGLU)
+//     that also emits the e4m3 activation and its amax;
+//   * device-side scheduler: every role walks the same static tile sequence blockIdx.x + i*gridDim.x and
+//     decodes (group, m-tile, n-tile) from prefix sums held in the kernel parameter block.  Tiles are
+//     ordered group-major and, inside a group, in super-rows of 32 m-tiles with m fastest, so the ~148
+//     concurrently running tiles share operand tiles through L2;
+//   * no cluster launch and no multicast: every CTA loads its own operands.
+// Two addressing modes share the kernel: "rows" (forward/dgrad: groups are row blocks of one A matrix,
+// B is (G,N,K)) and "wgrad" (each group has its own pair of TMA descriptors in global memory because the
+// padded-transposed operand blocks have a group-dependent row pitch; contraction length varies per group).
+//
+// Every wait on an mbarrier is bounded (about one second of wall clock); when it runs out the CTA
+// records a code in the device status word, raises a CTA-wide abort flag that all roles poll, drains and
+// frees its TMEM, and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace fp8gmm {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 128;  // bytes == fp8 elements
+constexpr int kStages = 4;
+constexpr int kSuperRows = 32;  // m-tiles per super-row of the tile order
+constexpr int kThreads = 192;
+constexpr int kTileABytes = kBlockM * kBlockK;          // 16 KiB
+constexpr int kTileBBytes = kBlockN * kBlockK;          // 32 KiB
+constexpr int kStageBytes = kTileABytes + kTileBBytes;  // 48 KiB
+constexpr int kTmemCols = 512;
+constexpr int kMaxGroups = 512;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+
+enum GemmMode { kModeRows = 0, kModeWgrad = 1 };
+
+struct GemmParams {
+  CUtensorMap map_a;          // kModeRows: A (sum m, K)
+  CUtensorMap map_b;          // kModeRows: B (G*N, K)
+  const CUtensorMap* maps;    // kModeWgrad: [2g] = A_t,g (N, L_g), [2g+1] = B_t,g (K, L_g)
+  uint16_t* c;
+  uint8_t* act_out;
+  const float* sa;
+  const float* sb;
+  const float* sc;
+  float* amax;
+  int64_t sa_stride, sb_stride, sc_stride, amax_stride;
+  int64_t ldc;     // row pitch of c in elements
+  int64_t ld_act;  // row pitch of act_out in bytes
+  int* status;
+  int mode;
+  int activation;
+  int num_groups;
+  int n;        // kModeRows: N (columns of C); kModeWgrad: K-dim of the weight (columns of C_g)
+  int m_fixed;  // kModeWgrad: rows of every C_g (= N of the layer)
+  int k;        // kModeRows: contraction length
+  int tiles_n;  // n-tiles per group
+  int total_tiles;
+  uint32_t idesc;
+  int tile_start[kMaxGroups + 1];  // prefix sum of tiles per group
+  int row_start[kMaxGroups + 1];   // kModeRows: prefix sum of rows; kModeWgrad: t_offsets (contraction offsets)
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false (after raising the CTA abort flag and recording `code`) when the barrier
+// did not complete its phase within kWaitLimitNs, or when another role already aborted.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      atomicOr(status, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane = row).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major operand tile written by TMA with SWIZZLE_128B:
+// rows are 128 bytes apart inside an 8-row swizzle atom, atoms are 1024 bytes apart (stride byte
+// offset); the leading byte offset is unused for swizzled K-major layouts.  Bits: [0,14) address>>4,
+// [16,30) LBO>>4, [32,46) SBO>>4, [46,48) descriptor version (1 on sm_100), [61,64) layout (2 = 128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  return 0.5f * x * (1.f + tanhf(0.79788456f * x * (1.f + 0.044715f * x * x)));
+}
+
+struct TileInfo {
+  int group, mt, nt;
+  int num_kb;      // K blocks of 128 bytes
+  int valid_rows;  // rows of this tile that belong to the output
+  int valid_cols;
+  int64_t row0;    // first output row (kModeRows: global row; kModeWgrad: row inside C_g)
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
+  TileInfo t;
+  const int g = upper_slot(p.tile_start, p.num_groups, tile);
+  const int local = tile - p.tile_start[g];
+  int rows_g, contraction;
+  if (p.mode == kModeRows) {
+    rows_g = p.row_start[g + 1] - p.row_start[g];
+    contraction = p.k;
+  } else {
+    rows_g = p.m_fixed;
+    contraction = p.row_start[g + 1] - p.row_start[g];
+  }
+  const int mt_g = (rows_g + kBlockM - 1) / kBlockM;
+  const int per_super = kSuperRows * p.tiles_n;
+  const int s = local / per_super;
+  const int rem = local - s * per_super;
+  const int h = min(kSuperRows, mt_g - s * kSuperRows);
+  t.group = g;
+  t.nt = rem / h;
+  t.mt = s * kSuperRows + rem % h;
+  t.num_kb = (contraction + kBlockK - 1) / kBlockK;
+  t.valid_rows = min(kBlockM, rows_g - t.mt * kBlockM);
+  const int tile_n = p.activation == FP8GMM_ACT_SWIGLU ? kBlockN / 2 : kBlockN;
+  const int n_cols = p.activation == FP8GMM_ACT_SWIGLU ? p.n / 2 : p.n;
+  t.valid_cols = min(tile_n, n_cols - t.nt * tile_n);
+  t.row0 = (p.mode == kModeRows ? static_cast<int64_t>(p.row_start[g]) : 0) + static_cast<int64_t>(t.mt) * kBlockM;
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;  // SWIZZLE_128B atoms need 1024-byte alignment
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + kStages * kStageBytes);
+  // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0 && p.mode == kModeRows) {
+      prefetch_tensormap(&p.map_a);
+      prefetch_tensormap(&p.map_b);
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = decode_tile(p, tile);
+      const CUtensorMap* map_a = p.mode == kModeRows ? &p.map_a : &p.maps[2 * t.group];
+      const CUtensorMap* map_b = p.mode == kModeRows ? &p.map_b : &p.maps[2 * t.group + 1];
+      int ya, yb0, yb1;
+      if (p.mode == kModeRows) {
+        ya = static_cast<int>(t.row0);
+        if (p.activation == FP8GMM_ACT_SWIGLU) {
+          yb0 = t.group * p.n + t.nt * (kBlockN / 2);  // gate rows
+          yb1 = yb0 + p.n / 2;                         // matching up rows
+        } else {
+          yb0 = t.group * p.n + t.nt * kBlockN;
+          yb1 = yb0 + kBlockN / 2;
+        }
+      } else {
+        ya = t.mt * kBlockM;
+        yb0 = t.nt * kBlockN;
+        yb1 = yb0 + kBlockN / 2;
+      }
+      for (int kb = 0; kb < t.num_kb && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x1);
+          if (ok) {
+            const uint32_t sa = tiles_addr + stage * kStageBytes;
+            const uint32_t sb = sa + kTileABytes;
+            mbar_expect_tx(full_bar(stage), kStageBytes);
+            tma_load_2d(sa, map_a, full_bar(stage), kb * kBlockK, ya);
+            tma_load_2d(sb, map_b, full_bar(stage), kb * kBlockK, yb0);
+            tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), kb * kBlockK, yb1);
+          }
+        }
+        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = decode_tile(p, tile);
+      if (t.num_kb == 0) continue;  // empty contraction: the epilogue writes zeros on its own
+      if (lane == 0) ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x2);
+      ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
+      for (int kb = 0; kb < t.num_kb && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, 0x4);
+          if (ok) {
+            tc_fence_after();
+            const uint32_t sa = tiles_addr + stage * kStageBytes;
+            const uint64_t da = make_smem_desc(sa);
+            const uint64_t db = make_smem_desc(sa + kTileABytes);
+#pragma unroll
+            for (int k = 0; k < kBlockK / 32; ++k) {
+              // advance both descriptors by 32 bytes (>>4 = 2) along K inside the swizzle atom
+              umma_f8(tmem_d, da + 2ull * k, db + 2ull * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar(stage));
+            if (kb == t.num_kb - 1) umma_commit(tfull_bar(acc));
+          }
+        }
+        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else {
+    // ===================== epilogue (warps 2..5) =====================
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const TileInfo t = decode_tile(p, tile);
+      const bool row_ok = row_in_tile < t.valid_rows;
+      const int64_t out_row = t.row0 + row_in_tile;
+      const float alpha = p.sa[t.group * p.sa_stride] * p.sb[t.group * p.sb_stride];
+      if (t.num_kb == 0) {
+        // nothing was accumulated: the product is exactly zero (wgrad of an empty group)
+        if (row_ok) {
+          uint16_t* dst = p.c + static_cast<int64_t>(t.group) * p.m_fixed * p.ldc + out_row * p.ldc + t.nt * kBlockN;
+          for (int c = 0; c < t.valid_cols; c += 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      if (lane == 0) ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x8);
+      ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quad * 32) << 16);
+
+      if (p.activation == FP8GMM_ACT_NONE) {
+        uint16_t* dst = p.c + (p.mode == kModeWgrad ? static_cast<int64_t>(t.group) * p.m_fixed * p.ldc : 0) +
+                        out_row * p.ldc + t.nt * kBlockN;
+        for (int c0 = 0; c0 < t.valid_cols; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (c0 + v * 8 < t.valid_cols) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
+                o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
+                o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
+                o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
+                *reinterpret_cast<uint4*>(dst + c0 + v * 8) = o;
+              }
+            }
+          }
+        }
+      } else if (p.activation == FP8GMM_ACT_GELU) {
+        const float sc = p.sc ? p.sc[t.group * p.sc_stride] : 1.f;
+        uint16_t* dst = p.c + out_row * p.ldc + t.nt * kBlockN;
+        uint8_t* adst = p.act_out + out_row * p.ld_act + t.nt * kBlockN;
+        float amax = 0.f;
+        for (int c0 = 0; c0 < t.valid_cols; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (c0 + v * 8 < t.valid_cols) {
+                float h[8], g[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  h[j] = __uint_as_float(r[v * 8 + j]) * alpha;
+                  g[j] = gelu_tanh(h[j]);
+                  amax = fmaxf(amax, fabsf(g[j]));
+                }
+                *reinterpret_cast<uint4*>(dst + c0 + v * 8) =
+                    make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+                *reinterpret_cast<uint2*>(adst + c0 + v * 8) =
+                    make_uint2(cvt_fp8x4<FP8GMM_E4M3>(g[0] * sc, g[1] * sc, g[2] * sc, g[3] * sc),
+                               cvt_fp8x4<FP8GMM_E4M3>(g[4] * sc, g[5] * sc, g[6] * sc, g[7] * sc));
+              }
+            }
+          }
+        }
+        if (p.amax) {
+          amax = warp_max(amax);
+          if (lane == 0) atomic_max_nonneg(p.amax + t.group * p.amax_stride, amax);
+        }
+      } else {  // SwiGLU: accumulator columns [0,128) = gate, [128,256) = up for the same 128 outputs
+        const float sc = p.sc ? p.sc[t.group * p.sc_stride] : 1.f;
+        const int half_n = p.n / 2;
+        uint16_t* dst_g = p.c + out_row * p.ldc + t.nt * (kBlockN / 2);
+        uint16_t* dst_u = dst_g + half_n;
+        uint8_t* adst = p.act_out + out_row * p.ld_act + t.nt * (kBlockN / 2);
+        float amax = 0.f;
+        for (int c0 = 0; c0 < t.valid_cols; c0 += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld32(taddr + c0, rg);
+          tmem_ld32(taddr + kBlockN / 2 + c0, ru);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (c0 + v * 8 < t.valid_cols) {
+                float hg[8], hu[8], a[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  hg[j] = __uint_as_float(rg[v * 8 + j]) * alpha;
+                  hu[j] = __uint_as_float(ru[v * 8 + j]) * alpha;
+                  a[j] = hg[j] / (1.f + __expf(-hg[j])) * hu[j];
+                  amax = fmaxf(amax, fabsf(a[j]));
+                }
+                *reinterpret_cast<uint4*>(dst_g + c0 + v * 8) =
+                    make_uint4(pack_bf16x2(hg[0], hg[1]), pack_bf16x2(hg[2], hg[3]), pack_bf16x2(hg[4], hg[5]), pack_bf16x2(hg[6], hg[7]));
+                *reinterpret_cast<uint4*>(dst_u + c0 + v * 8) =
+                    make_uint4(pack_bf16x2(hu[0], hu[1]), pack_bf16x2(hu[2], hu[3]), pack_bf16x2(hu[4], hu[5]), pack_bf16x2(hu[6], hu[7]));
+                *reinterpret_cast<uint2*>(adst + c0 + v * 8) =
+                    make_uint2(cvt_fp8x4<FP8GMM_E4M3>(a[0] * sc, a[1] * sc, a[2] * sc, a[3] * sc),
+                               cvt_fp8x4<FP8GMM_E4M3>(a[4] * sc, a[5] * sc, a[6] * sc, a[7] * sc));
+              }
+            }
+          }
+        }
+        if (p.amax) {
+          amax = warp_max(amax);
+          if (lane == 0) atomic_max_nonneg(p.amax + t.group * p.amax_stride, amax);
+        }
+      }
+      // hand the accumulator back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ===================== teardown =====================
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies and MMAs that are still in flight time to land before shared memory and TMEM go away.
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// 2-D uint8 tensor (rows x cols bytes, row pitch = cols), box 128 rows x 128 bytes, SWIZZLE_128B.
+int encode_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+  auto fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return FP8GMM_CUDA_ERROR;
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {kBlockK, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with %d (base %p, rows %llu, cols %llu)", static_cast<int>(r), base,
+              static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols));
+    return FP8GMM_CUDA_ERROR;
+  }
+  return FP8GMM_OK;
+}
+
+uint32_t make_idesc(int a_format, int b_format) {
+  // tcgen05 instruction descriptor, kind::f8f6f4: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format
+  // (0 = e4m3, 1 = e5m2), bits 15/16 = 0 (both operands K-major), [17,23) N >> 3, [24,29) M >> 4.
+  uint32_t d = 0;
+  d |= 1u << 4;
+  d |= static_cast<uint32_t>(a_format) << 7;
+  d |= static_cast<uint32_t>(b_format) << 10;
+  d |= static_cast<uint32_t>(kBlockN >> 3) << 17;
+  d |= static_cast<uint32_t>(kBlockM >> 4) << 24;
+  return d;
+}
+
+int launch(const GemmParams& p, cudaStream_t s) {
+  // The attribute is per device and the call is idempotent and cheap, so it is simply repeated.
+  FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, s>>>(p);
+  FP8GMM_CHECK_CUDA(cudaGetLastError());
+  return FP8GMM_OK;
+}
+
+bool fmt_ok(int f) { return f == FP8GMM_E4M3 || f == FP8GMM_E5M2; }
+
+}  // namespace
+}  // namespace fp8gmm
+
+extern "C" {
+
+int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(a != nullptr, "grouped_gemm: NULL arguments");
+  FP8GMM_CHECK_ARG(a->num_groups >= 0 && a->num_groups <= kMaxGroups, "grouped_gemm: num_groups %d outside [0, %d]",
+                   a->num_groups, kMaxGroups);
+  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_gemm: bad fp8 format");
+  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
+                   "grouped_gemm: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n, (long long)a->k);
+  FP8GMM_CHECK_ARG(a->activation >= 0 && a->activation <= 2, "grouped_gemm: bad activation %d", a->activation);
+  if (a->num_groups == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(a->m_sizes != nullptr, "grouped_gemm: NULL m_sizes");
+  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_gemm: NULL scale_inv pointer");
+  if (a->activation != FP8GMM_ACT_NONE) {
+    FP8GMM_CHECK_ARG(a->act_out != nullptr, "grouped_gemm: activation requested without act_out");
+    FP8GMM_CHECK_ARG(a->activation != FP8GMM_ACT_SWIGLU || a->n % 32 == 0, "grouped_gemm: SwiGLU needs N %% 32 == 0");
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int tile_n = a->activation == FP8GMM_ACT_SWIGLU ? kBlockN / 2 : kBlockN;
+  const int64_t n_cols = a->activation == FP8GMM_ACT_SWIGLU ? a->n / 2 : a->n;
+  const int64_t tiles_n = (n_cols + tile_n - 1) / tile_n;
+  int64_t rows = 0, tiles = 0;
+  p.tile_start[0] = 0;
+  p.row_start[0] = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t m = a->m_sizes[g];
+    FP8GMM_CHECK_ARG(m >= 0, "grouped_gemm: m_sizes[%d] is negative", g);
+    rows += m;
+    tiles += ((m + kBlockM - 1) / kBlockM) * tiles_n;
+    FP8GMM_CHECK_ARG(rows <= INT32_MAX - 1024 && tiles <= INT32_MAX / 2, "grouped_gemm: problem too large");
+    p.row_start[g + 1] = static_cast<int>(rows);
+    p.tile_start[g + 1] = static_cast<int>(tiles);
+  }
+  if (rows == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(a->a && a->b && a->c, "grouped_gemm: NULL operand pointer");
+  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a) | reinterpret_cast<uintptr_t>(a->b) |
+                    reinterpret_cast<uintptr_t>(a->c) | reinterpret_cast<uintptr_t>(a->act_out)) % 16 == 0,
+                   "grouped_gemm: operand pointers must be 16-byte aligned");
+  FP8GMM_CHECK_ARG(static_cast<int64_t>(a->num_groups) * a->n <= INT32_MAX - 1024, "grouped_gemm: G*N too large");
+  int rc = encode_map(&p.map_a, a->a, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->k));
+  if (rc != FP8GMM_OK) return rc;
+  rc = encode_map(&p.map_b, a->b, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
+  if (rc != FP8GMM_OK) return rc;
+  p.maps = nullptr;
+  p.c = static_cast<uint16_t*>(a->c);
+  p.act_out = static_cast<uint8_t*>(a->act_out);
+  p.sa = a->a_scale_inv;
+  p.sb = a->b_scale_inv;
+  p.sc = a->act_scale;
+  p.amax = a->act_amax;
+  p.sa_stride = a->a_scale_inv_stride;
+  p.sb_stride = a->b_scale_inv_stride;
+  p.sc_stride = a->act_scale_stride;
+  p.amax_stride = a->act_amax_stride;
+  p.ldc = a->n;
+  p.ld_act = n_cols;
+  p.status = device_status_word();
+  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_gemm: cannot resolve the device status word");
+  p.mode = kModeRows;
+  p.activation = a->activation;
+  p.num_groups = a->num_groups;
+  p.n = static_cast<int>(a->n);
+  p.m_fixed = 0;
+  p.k = static_cast<int>(a->k);
+  p.tiles_n = static_cast<int>(tiles_n);
+  p.total_tiles = static_cast<int>(tiles);
+  p.idesc = make_idesc(a->a_format, a->b_format);
+  return launch(p, static_cast<cudaStream_t>(stream));
+}
+
+size_t fp8gmm_wgrad_workspace_bytes(int num_groups) {
+  return num_groups > 0 ? static_cast<size_t>(num_groups) * 2 * sizeof(CUtensorMap) : 0;
+}
+
+int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(a != nullptr, "grouped_wgrad: NULL arguments");
+  FP8GMM_CHECK_ARG(a->num_groups >= 0 && a->num_groups <= kMaxGroups, "grouped_wgrad: num_groups %d outside [0, %d]",
+                   a->num_groups, kMaxGroups);
+  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_wgrad: bad fp8 format");
+  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
+                   "grouped_wgrad: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n, (long long)a->k);
+  if (a->num_groups == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "grouped_wgrad: NULL pointer");
+  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_wgrad: NULL scale_inv pointer");
+  FP8GMM_CHECK_ARG(a->workspace != nullptr && a->workspace_bytes >= fp8gmm_wgrad_workspace_bytes(a->num_groups),
+                   "grouped_wgrad: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes,
+                   fp8gmm_wgrad_workspace_bytes(a->num_groups));
+  FP8GMM_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 128 == 0, "grouped_wgrad: workspace must be 128-byte aligned");
+  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
+                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0, "grouped_wgrad: operand pointers must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int64_t tiles_m = (a->n + kBlockM - 1) / kBlockM;
+  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
+  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad: problem too large");
+  std::vector<CUtensorMap> maps(static_cast<size_t>(a->num_groups) * 2);
+  memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
+  p.tile_start[0] = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
+    const int64_t len = o1 - o0;
+    FP8GMM_CHECK_ARG(len >= 0 && len % 16 == 0 && o1 <= INT32_MAX - 1024,
+                     "grouped_wgrad: group %d contraction length %lld must be a non-negative multiple of 16", g,
+                     (long long)len);
+    p.row_start[g] = static_cast<int>(o0);
+    p.row_start[g + 1] = static_cast<int>(o1);
+    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
+    if (len > 0) {
+      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "grouped_wgrad: NULL operand pointer");
+      int rc = encode_map(&maps[2 * g], static_cast<const char*>(a->a_t) + o0 * a->n, static_cast<uint64_t>(a->n),
+                          static_cast<uint64_t>(len));
+      if (rc != FP8GMM_OK) return rc;
+      rc = encode_map(&maps[2 * g + 1], static_cast<const char*>(a->b_t) + o0 * a->k, static_cast<uint64_t>(a->k),
+                      static_cast<uint64_t>(len));
+      if (rc != FP8GMM_OK) return rc;
+    }
+  }
+  // Pageable source: the runtime stages the bytes before returning, so `maps` may go out of scope.
+  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(a->workspace, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
+  p.maps = static_cast<const CUtensorMap*>(a->workspace);
+  p.c = static_cast<uint16_t*>(a->c);
+  p.sa = a->a_scale_inv;
+  p.sb = a->b_scale_inv;
+  p.sa_stride = a->a_scale_inv_stride;
+  p.sb_stride = a->b_scale_inv_stride;
+  p.ldc = a->k;
+  p.status = device_status_word();
+  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_wgrad: cannot resolve the device status word");
+  p.mode = kModeWgrad;
+  p.activation = FP8GMM_ACT_NONE;
+  p.num_groups = a->num_groups;
+  p.n = static_cast<int>(a->k);
+  p.m_fixed = static_cast<int>(a->n);
+  p.k = 0;
+  p.tiles_n = static_cast<int>(tiles_n);
+  p.total_tiles = p.tile_start[a->num_groups];
+  p.idesc = make_idesc(a->a_format, a->b_format);
+  return launch(p, s);
+}
+
+}  // extern "C"

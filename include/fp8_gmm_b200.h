@@ -1,0 +1,244 @@
+/*
+ * fp8_gmm_b200 -- C ABI of the B200 (sm_100a) FP8 grouped-GEMM library.
+ *
+ * This header is the drop-in boundary: every entry point replaces one function of the reference's
+ * pybind11 module `fp8_gmm_backend` (reference csrc/ops.cu:9-16) or one library call the reference
+ * reaches through Transformer Engine.  Signatures use plain pointers and sizes only: no torch, no
+ * pybind, no C++ types.  All device pointers are borrowed for the duration of the enqueued work;
+ * the caller keeps the memory alive and orders other streams against `stream` itself.
+ *
+ * Conventions
+ *   - every function returns 0 on success and a non-zero fp8gmm_status otherwise; it never throws,
+ *     aborts or synchronises the device (except fp8gmm_device_status, which says so);
+ *     fp8gmm_last_error() gives a thread-local message for the last non-zero return;
+ *   - `stream` is a cudaStream_t passed as void*; NULL means the legacy default stream;
+ *   - fp8 buffers are raw bytes in the OCP formats E4M3 (finite-only, max 448) and E5M2 (max 57344);
+ *   - "scale" pointers are device fp32; a NULL scale pointer means 1.0; amax pointers may be NULL;
+ *   - per-group fp32 metadata is addressed as base[g * stride] (stride in elements), which is how the
+ *     reference indexes Transformer Engine's meta vectors (reference fp8_gmm/utils.py:98-103).
+ */
+#ifndef FP8_GMM_B200_H_
+#define FP8_GMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FP8GMM_OK = 0,
+  FP8GMM_INVALID_ARGUMENT = 1, /* shape / alignment / NULL-pointer contract violated; nothing was launched */
+  FP8GMM_CUDA_ERROR = 2,       /* a CUDA runtime or driver call failed; see fp8gmm_last_error() */
+  FP8GMM_UNSUPPORTED = 3,      /* device is not sm_100, or a size exceeds a documented limit */
+  FP8GMM_DEVICE_TIMEOUT = 4    /* reported by fp8gmm_device_status(): a bounded wait in a kernel ran out */
+} fp8gmm_status;
+
+typedef enum { FP8GMM_E4M3 = 0, FP8GMM_E5M2 = 1 } fp8gmm_format;
+
+typedef enum { FP8GMM_ACT_NONE = 0, FP8GMM_ACT_GELU = 1, FP8GMM_ACT_SWIGLU = 2 } fp8gmm_activation;
+
+/* Library version (major * 1000 + minor). */
+int fp8gmm_version(void);
+
+/* Thread-local, NUL-terminated description of the last failure on this thread ("" if none). */
+const char* fp8gmm_last_error(void);
+
+/*
+ * Synchronises `stream`, then reads and clears the device-side status word of the current device.
+ * Returns FP8GMM_OK, FP8GMM_DEVICE_TIMEOUT (a kernel gave up on a bounded wait and returned without
+ * finishing; outputs of that launch are undefined) or FP8GMM_CUDA_ERROR.  Meant for tests and
+ * debugging; the hot path does not call it.
+ */
+int fp8gmm_device_status(void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Multi-tensor elementwise kernels (HBM-bound).
+ *
+ * One descriptor per tensor; any number of tensors per call (the reference caps a call at 64:
+ * csrc/multi_pointwise.cu:13, csrc/multi_pad_fusion.cu:14).  Descriptors live in host memory and are
+ * consumed before the function returns.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* in;      /* (rows x cols) row-major: bf16 for the cast ops, fp8 for fp8gmm_multi_pad_transpose */
+  const void* in2;     /* dgelu: pre-activation bf16 (rows x cols); dswiglu: pre-activation bf16 (rows x 2*cols); else NULL */
+  void* out;           /* fp8 (rows x cols) [dswiglu: (rows x 2*cols)], or NULL to skip */
+  void* out_t;         /* fp8 (cols x padded_rows) [dswiglu: (2*cols x padded_rows)], rows >= `rows` are padding; or NULL */
+  const float* scale;  /* device fp32, NULL = 1.0 */
+  float* amax;         /* device fp32, max-merged: *amax = max(*amax, max|x|) over the unscaled values; or NULL */
+  int64_t rows;
+  int64_t cols;
+  int64_t padded_rows; /* >= rows; ignored when out_t is NULL */
+} fp8gmm_tensor_desc;
+
+/*
+ * bf16 -> fp8 `OType(scale * fp32(x))` (round-to-nearest-even, saturating) + amax, flat over
+ * rows*cols elements; `in2`, `out_t`, `padded_rows` are ignored.  `out` may be NULL (amax only).
+ * Replaces MultiQuantize (reference csrc/multi_pointwise.h:9-11, csrc/multi_pointwise.cu:155-214).
+ */
+int fp8gmm_multi_quantize(const fp8gmm_tensor_desc* descs, int count, int out_format, void* stream);
+
+/*
+ * fp8 -> fp8 transpose into (cols x padded_rows) with zero bytes in the padding.
+ * Replaces MultiPadTranspose (reference csrc/multi_pad_fusion.h:9-11, csrc/multi_pad_fusion.cu:442-503).
+ */
+int fp8gmm_multi_pad_transpose(const fp8gmm_tensor_desc* descs, int count, void* stream);
+
+/*
+ * bf16 -> fp8 cast written twice (same shape to `out`, padded transpose to `out_t`) + amax.
+ * Padding bytes are `OType(scale * 0)` exactly as in the reference.
+ * Replaces MultiPadCastTranspose (reference csrc/multi_pad_fusion.h:13-19, csrc/multi_pad_fusion.cu:505-585).
+ */
+int fp8gmm_multi_pad_cast_transpose(const fp8gmm_tensor_desc* descs, int count, int out_format, void* stream);
+
+/*
+ * As above with x = in * dgelu_tanh(in2) fused in front of the cast (amax over x).
+ * Replaces MultiPadCastTransposeDgelu (reference csrc/multi_pad_fusion.h:21-23, csrc/multi_pad_fusion.cu:587-670).
+ */
+int fp8gmm_multi_pad_cast_transpose_dgelu(const fp8gmm_tensor_desc* descs, int count, int out_format, void* stream);
+
+/*
+ * SwiGLU backward fused in front of the cast: in = d(act) (rows x cols), in2 = pre-activation
+ * h = [gate | up] (rows x 2*cols); writes d(h) = [d gate | d up] as fp8 (rows x 2*cols) and its padded
+ * transpose (2*cols x padded_rows); one amax over d(h).  No counterpart in the reference (it has
+ * GELU only, reference fp8_gmm/grouped_mlp.py:254-287); modelled on the dgelu entry point.
+ */
+int fp8gmm_multi_pad_cast_transpose_dswiglu(const fp8gmm_tensor_desc* descs, int count, int out_format, void* stream);
+
+typedef struct {
+  void* data;          /* bf16, updated in place */
+  const float* scale1; /* device fp32, NULL = 1.0 */
+  const float* scale2; /* device fp32, NULL = 1.0 */
+  int64_t numel;
+} fp8gmm_scale_mul_desc;
+
+/*
+ * In place x = bf16(fp32(x) * scale1 * scale2).
+ * Replaces MultiScaleMul (reference csrc/multi_pointwise.h:13-15, csrc/multi_pointwise.cu:216-259).
+ */
+int fp8gmm_multi_scale_mul(const fp8gmm_scale_mul_desc* descs, int count, void* stream);
+
+/*
+ * Grouped convenience form of fp8gmm_multi_pad_cast_transpose for the layout the modules use
+ * (reference fp8_gmm/grouped_linear.py:32-52,133-149): `in` is one (sum rows x cols) bf16 matrix whose
+ * row blocks are the groups; group g is cast into out[row_offsets[g]..] and, when out_t != NULL,
+ * transposed into the block of out_t that starts at byte t_offsets[g] * cols and holds
+ * (cols x (t_offsets[g+1] - t_offsets[g])) bytes.  row_offsets / t_offsets are host arrays of
+ * num_groups + 1 prefix sums.  in2 / activation select the fused backward variants (0 none, 1 dgelu,
+ * 2 dswiglu); scale and amax are addressed as base[g * stride].
+ */
+typedef struct {
+  const void* in;
+  const void* in2;
+  void* out;
+  void* out_t;
+  const int64_t* row_offsets;
+  const int64_t* t_offsets;
+  int num_groups;
+  int64_t cols;
+  const float* scale;
+  int64_t scale_stride;
+  float* amax;
+  int64_t amax_stride;
+  int out_format;
+  int activation;
+  int in_is_fp8; /* 1: `in` is already fp8 and the call is a pure padded transpose (scale/amax/out ignored) */
+} fp8gmm_grouped_cast_args;
+
+int fp8gmm_grouped_pad_cast_transpose(const fp8gmm_grouped_cast_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Grouped GEMM (tensor-core bound): tcgen05 / TMEM kernel with TMA-fed FP8 tiles.
+ * ---------------------------------------------------------------------------------------------- */
+
+/*
+ * Forward / dgrad:  C_g = act( (A_g B_g^T) * a_scale_inv[g] * b_scale_inv[g] )  for every group g.
+ *   a        fp8 (sum m x K) row-major, groups are consecutive row blocks of m_sizes[g] rows
+ *   b        fp8 (G x N x K) row-major ("column-major B", both operands K-major)
+ *   c        bf16 (sum m x N): the (de-scaled) product, or the pre-activation when activation != NONE
+ *   m_sizes  HOST int64[num_groups] (the reference requires a CPU tensor, csrc/fp8_gmm.cu:165-167);
+ *            zero-sized groups are allowed
+ *   activation != NONE additionally writes act_out = e4m3( act(.) * act_scale[g] ) and merges
+ *            max|act(.)| into act_amax[g]: GELU: act_out is (sum m x N); SWIGLU: b holds [gate rows |
+ *            up rows] (N = 2F) and act_out is (sum m x N/2).
+ * N and K must be multiples of 16 (the reference assumes the same: fp8_gmm/grouped_linear.py:69).
+ * Replaces Fp8GroupedGemm + MultiScaleMul (reference csrc/fp8_gmm.h:7-11, csrc/fp8_gmm.cu:163-205,
+ * fp8_gmm/backend.py:78-82) and the per-group te_gemm loop with its GELU-aux epilogue (reference
+ * fp8_gmm/backend.py:26-54,84-96).
+ */
+typedef struct {
+  const void* a;
+  const void* b;
+  void* c;
+  const int64_t* m_sizes;
+  int num_groups;
+  int64_t n;
+  int64_t k;
+  int a_format;
+  int b_format;
+  const float* a_scale_inv;
+  int64_t a_scale_inv_stride;
+  const float* b_scale_inv;
+  int64_t b_scale_inv_stride;
+  int activation;
+  void* act_out;
+  const float* act_scale;
+  int64_t act_scale_stride;
+  float* act_amax;
+  int64_t act_amax_stride;
+} fp8gmm_gemm_args;
+
+int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* args, void* stream);
+
+/*
+ * Weight gradient, one launch for all groups:
+ *   C_g (N x K) = (A_t,g  B_t,g^T) * a_scale_inv[g] * b_scale_inv[g]
+ * on the padded-transposed operands the cast kernels produce:
+ *   a_t  fp8, group g is an (N x L_g) row-major block at byte offset t_offsets[g] * N
+ *   b_t  fp8, group g is a  (K x L_g) row-major block at byte offset t_offsets[g] * K
+ *   L_g = t_offsets[g+1] - t_offsets[g] must be a multiple of 16; L_g = 0 gives C_g = 0
+ *   c    bf16 (G x N x K)
+ *   t_offsets  HOST int64[num_groups + 1]
+ * `workspace` is device memory of at least fp8gmm_wgrad_workspace_bytes(num_groups) bytes, 128-byte
+ * aligned, owned by the caller and reusable as soon as work enqueued on `stream` after this call runs;
+ * the call fills it with per-group TMA descriptors by an asynchronous copy on `stream`.
+ * Replaces the per-group cublas_fp8_gemm wgrad loop (reference fp8_gmm/grouped_linear.py:165-182,
+ * fp8_gmm/grouped_mlp.py:226-242,304-322).
+ */
+typedef struct {
+  const void* a_t;
+  const void* b_t;
+  void* c;
+  const int64_t* t_offsets;
+  int num_groups;
+  int64_t n;
+  int64_t k;
+  int a_format;
+  int b_format;
+  const float* a_scale_inv;
+  int64_t a_scale_inv_stride;
+  const float* b_scale_inv;
+  int64_t b_scale_inv_stride;
+  void* workspace;
+  size_t workspace_bytes;
+} fp8gmm_wgrad_args;
+
+size_t fp8gmm_wgrad_workspace_bytes(int num_groups);
+int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Delayed-scaling recipe update (the Transformer Engine hook the reference relies on through
+ * prepare_forward, reference fp8_gmm/grouped_linear.py:206): for each of `n` metas
+ *   amax = max over history rows (algo 0) or history row 0 (algo 1);
+ *   scale = fp8_max / amax / 2^margin where amax is positive and finite, else unchanged;
+ *   scale_inv = 1 / scale; history rolled by one row with row 0 zeroed.
+ * amax_history is (history_len x n) fp32 row-major, updated in place.
+ * ---------------------------------------------------------------------------------------------- */
+int fp8gmm_delayed_scaling_update(float* amax_history, float* scale, float* scale_inv, int history_len, int n,
+                                  float fp8_max, float margin, int algo, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP8_GMM_B200_H_ */

@@ -1,0 +1,56 @@
+"""CPU: host-side bookkeeping that defines layouts and meta slots (reference fp8_gmm/utils.py)."""
+import torch
+
+from fp8_gmm_b200 import recipe, utils
+from oracle import oracle as O
+
+
+def test_cumsum_group_sizes_matches_reference_semantics():
+    # reference fp8_gmm/utils.py:48-62
+    assert utils.cumsum_group_sizes([128, 96, 160, 128], need_padding=True) == (4, False, [0, 128, 224, 384, 512], [0, 128, 224, 384, 512])
+    assert utils.cumsum_group_sizes([5, 0, 33], need_padding=True) == (3, True, [0, 5, 5, 38], [0, 16, 16, 64])
+    assert utils.cumsum_group_sizes([5, 0, 33]) == (3, False, [0, 5, 5, 38], None)
+    assert utils.cumsum_group_sizes([]) == (0, False, [0], None)
+    for sizes in ([1, 2, 3], [16, 32], [0, 0], [4095, 17, 1]):
+        assert utils.cumsum_group_sizes(sizes, True) == O.cumsum_group_sizes(sizes, True)
+
+
+class _Meta:
+    def __init__(self, n, hist=2):
+        self.scale = torch.arange(n, dtype=torch.float32)
+        self.scale_inv = torch.arange(n, dtype=torch.float32) + 100
+        self.amax_history = torch.arange(hist * n, dtype=torch.float32).reshape(hist, n) + 1000
+
+
+def test_meta_slots():
+    # reference fp8_gmm/utils.py:98-103: slot = (group_offset + i) * stage + type
+    G = 3
+    meta = {"scaling_fwd": _Meta(3 * 2 * G), "scaling_bwd": _Meta(2 * 2 * G)}
+    w = utils.Fp8MetaWrapper(G, meta)
+    T, M = utils.Fp8TensorType, utils.MetaTensorType
+    get = lambda t, m: [float(v) for v in w.get_meta_tensors(t, m)]  # noqa: E731
+    assert get(T.kInputGroup1, M.kScale) == [0, 3, 6]
+    assert get(T.kWeightGroup1, M.kScale) == [1, 4, 7]
+    assert get(T.kInputGroup2, M.kScale) == [9, 12, 15]
+    assert get(T.kWeightGroup2, M.kScaleInv) == [110, 113, 116]
+    assert get(T.kGradOutputGroup1, M.kScale) == [0, 2, 4]
+    assert get(T.kGradOutputGroup2, M.kAmax) == [1006, 1008, 1010]
+    w.set_forward_scale_inv_cloned()
+    meta["scaling_fwd"].scale_inv += 1  # later updates must not leak into the snapshot
+    assert get(T.kForwardInputGroup1, M.kScaleInv) == [100, 103, 106]
+    assert get(T.kForwardWeightGroup2, M.kScaleInv) == [110, 113, 116]
+    # strided form addresses the same slots
+    for t, m in [(T.kInputGroup2, M.kScale), (T.kGradOutputGroup2, M.kAmax), (T.kForwardWeightGroup1, M.kScaleInv)]:
+        base, stride = w.get_meta_strided(t, m)
+        assert [float(base[i * stride]) for i in range(G)] == get(t, m)
+
+
+def test_dtype_maps_and_recipe_formats():
+    assert utils.to_torch_dtype(utils.to_tex_dtype(torch.float8_e5m2)) == torch.float8_e5m2
+    r = recipe.DelayedScaling(fp8_format=recipe.Format.HYBRID)
+    assert recipe.get_fp8_te_dtype(r, True) == utils.DType.kFloat8E4M3
+    assert recipe.get_fp8_te_dtype(r, False) == utils.DType.kFloat8E5M2
+    assert recipe.get_fp8_te_dtype(recipe.DelayedScaling(fp8_format=recipe.Format.E4M3), False) == utils.DType.kFloat8E4M3
+    with recipe.fp8_autocast(enabled=True, fp8_recipe=recipe.DelayedScaling(amax_history_len=16)):
+        assert recipe.is_fp8_enabled() and recipe.get_fp8_recipe().amax_history_len == 16
+    assert not recipe.is_fp8_enabled()
