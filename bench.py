@@ -1,0 +1,323 @@
+"""Benchmark of the FP8 grouped-MLP hot path: forward + dgrad + wgrad on synthetic data.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One process per GPU (launched under torch.distributed.run for N > 1).  A "step" is one forward +
+backward of GroupedMlp over one routed batch.  Prints ONE JSON line on rank 0:
+
+* ``value``      TFLOP/s with inputs resident in HBM (algorithmic FLOPs 18 * rows * hidden * ffn for SwiGLU,
+                 true rows, padding not counted), CUDA-event timed, max over ranks;
+* ``e2e``        same metric through the public module API with HOST buffers: every step copies the step's
+                 inputs (x, grad_out) from pinned host memory and reads the results (out, grad_input) back;
+* ``roofline``   the dominant kernel (the tcgen05 grouped GEMM, 6 launches per step): algorithmic FLOPs per
+                 launch / mean launch duration from CUDA events recorded around each launch inside the timed
+                 region, against 2 x the measured dense bf16 rate (dense FP8 is twice bf16 on this part);
+* ``cpu_baseline`` the CPU oracle (torch per-group float8-emulated matmuls + CPU quantise/transposes)
+                 timed on the host cores on a bounded sample of the same workload.
+
+``--impl reference`` times that CPU path alone (the reference has no CPU or sm_100 implementation of
+its own: its GEMM is Hopper-only CUTLASS and its other GEMM path needs Transformer Engine, so the
+float8-emulated per-group matmul loop of its test-suite is what can run on host cores).
+
+Workloads (synthetic, seeded): N = 1 -> Mixtral-8x7B-shaped MLP (8 experts, hidden 4096, ffn 14336,
+SwiGLU, 16384 tokens top-2 = 32768 routed rows, multinomial routing over softmax(N(0,1)) logits);
+N > 1 -> expert parallelism (128 experts split over the ranks, hidden 4096, ffn 1536, 32768 tokens per
+GPU top-8, all-to-all dispatch/combine over NCCL).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "grouped_mlp_fwd_bwd_fp8_tflops"
+NOMINAL_FP8_TFLOPS = 4500.0
+# DRAM bytes (read + write) per GEMM launch, averaged over the six launches of one Mixtral-shaped step,
+# from the ncu capture summarised in profiles/ (None until a capture exists).
+GEMM_DRAM_BYTES_PER_LAUNCH = None
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=8)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default="auto", choices=["auto", "mixtral", "ep"])
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    return p.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+def mixtral_workload(seed=0):
+    E, H, F, tokens, topk = 8, 4096, 14336, 16384, 2
+    g = torch.Generator().manual_seed(seed)
+    probs = torch.softmax(torch.randn(tokens, E, generator=g), dim=-1)
+    picks = torch.multinomial(probs, topk, replacement=False, generator=g)  # (tokens, 2) distinct experts
+    sizes = torch.bincount(picks.reshape(-1), minlength=E)
+    return dict(name="mixtral-8x7b-shaped GroupedMLP (E=8, hidden 4096, ffn 14336, SwiGLU, 16384 tokens top-2)",
+                E=E, H=H, F=F, tokens=tokens, topk=topk, sizes=sizes, rows=int(sizes.sum()))
+
+
+def mlp_flops(rows, H, F):
+    return 18.0 * rows * H * F  # SwiGLU: fc1 is H -> 2F; fwd + dgrad + wgrad = 3 x (2*rows*H*2F + 2*rows*F*H)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        mhz = sorted(int(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU path (oracle port) -- the baseline arm
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_step(H, F_full, rows_per_expert, seed=0):
+    """Returns (callable running one CPU step on the sample, flops of the sample, description)."""
+    from oracle import oracle as O
+
+    rows, F = max(64, rows_per_expert // 8), F_full // 8
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, H, generator=g).to(torch.bfloat16)
+    dy = torch.randn(rows, H, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(1, 2 * F, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(1, H, F, generator=g) * 0.02).to(torch.bfloat16)
+    one = [1.0]
+    scales = dict(x=one, w1=one, act=one, w2=one, dy=one, dpre=one)
+
+    def step():
+        return O.grouped_mlp_step(x, w1, w2, dy, [rows], scales, act="swiglu")
+
+    desc = (f"1 expert, {rows} rows, hidden {H}, ffn slice {F} of {F_full} (same rows:weights ratio as the full "
+            f"step), full fwd+bwd incl. quantise/transposes, torch CPU float8-emulated matmuls")
+    return step, mlp_flops(rows, H, F), desc
+
+
+def run_cpu(step, flops, reps, warmup):
+    torch.set_num_threads(os.cpu_count() or 1)
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    mean = sum(times) / len(times)
+    return flops / mean / 1e12, mean
+
+
+def reference_arm(args, wl_desc, H, F, rows_per_expert):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, flops, desc = cpu_sample_step(H, F, rows_per_expert)
+    tflops, mean = run_cpu(step, flops, args.steps, args.warmup)
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8 (e4m3 fwd / e5m2 grad, fp32 accumulate; float8-emulated on CPU)",
+        "data": "synthetic", "config": {"workload": wl_desc, "sample": desc},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm, N = 1
+# ------------------------------------------------------------------------------------------------
+def timed_steps(fn, steps):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / 1e3  # seconds
+
+
+def run_single(args):
+    import fp8_gmm_b200 as fg
+    from fp8_gmm_b200 import backend
+
+    wl = mixtral_workload()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    E, H, F, rows = wl["E"], wl["H"], wl["F"], wl["rows"]
+    sizes = wl["sizes"]
+    g = torch.Generator().manual_seed(1)
+    x_host = torch.randn(rows, H, generator=g).to(torch.bfloat16).pin_memory()
+    dy_host = torch.randn(rows, H, generator=g).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
+    gi_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
+    torch.manual_seed(2)
+    mlp = fg.GroupedMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu")
+    with torch.no_grad():
+        mlp.fc1_weight.normal_(0.0, 0.02)
+        mlp.fc2_weight.normal_(0.0, 0.02)
+    x_dev = x_host.to(dev).requires_grad_(True)
+    dy_dev = dy_host.to(dev)
+    recipe = fg.DelayedScaling(amax_history_len=16)
+
+    def step():
+        mlp.fc1_weight.grad = None
+        mlp.fc2_weight.grad = None
+        x_dev.grad = None
+        with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+            out = mlp(x_dev, sizes)
+        out.backward(dy_dev)
+        return out
+
+    def step_e2e():
+        x_dev.data.copy_(x_host, non_blocking=True)
+        dy_dev.copy_(dy_host, non_blocking=True)
+        out = step()
+        out_host.copy_(out.detach(), non_blocking=True)
+        gi_host.copy_(x_dev.grad, non_blocking=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    backend.device_status()
+
+    flops = mlp_flops(rows, H, F)
+    timings = []
+    backend.set_gemm_timings(timings)
+    launches0 = backend.launch_count()
+    with ClockSampler(dev.index or 0) as clocks:
+        secs = timed_steps(step, args.steps)
+    launches = backend.launch_count() - launches0
+    backend.set_gemm_timings(None)
+    gemm_ms = sum(s.elapsed_time(e) for s, e, _ in timings)
+    gemm_flops = flops * args.steps  # all of a step's algorithmic FLOPs are in its six GEMM launches
+    n_gemm = len(timings)
+
+    for _ in range(2):
+        step_e2e()
+    secs_e2e = timed_steps(step_e2e, args.steps)
+    backend.device_status()
+
+    peaks = measured_peaks()
+    peak_fp8 = 2.0 * peaks["bf16_sustained"]
+    value = flops * args.steps / secs / 1e12
+    achieved = gemm_flops / (gemm_ms / 1e3) / 1e12
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8 (e4m3 fwd / e5m2 grad, fp32 accumulate in TMEM, bf16 out)", "data": "synthetic",
+        "config": {"workload": wl["name"], "routed_rows": rows, "group_sizes": sizes.tolist(),
+                   "l2": "operands (2.8 GB of weights + 0.8 GB of activations per step) far exceed the 126 MB L2",
+                   "recipe": "delayed scaling, amax history 16"},
+        "tokens_per_s": wl["tokens"] * args.steps / secs,
+        "frac_of_nominal_fp8_peak": value / NOMINAL_FP8_TFLOPS,
+        "clocks": clocks.summary(),
+        "e2e": {"value": flops * args.steps / secs_e2e / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": x_host.numel() * 2 + dy_host.numel() * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2 + gi_host.numel() * 2,
+                "ms_per_step": secs_e2e / args.steps * 1e3},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "grouped_gemm_kernel (tcgen05, 6 launches per step)", "bound": "tensor",
+                     "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s", "frac": achieved / peak_fp8,
+                     "peak_source": f"2 x {peaks['source']} dense bf16 sustained ({peaks['bf16_sustained']} TFLOP/s)",
+                     "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                     "launches_timed": n_gemm, "mean_launch_ms": gemm_ms / max(n_gemm, 1),
+                     "flops_per_launch": gemm_flops / max(n_gemm, 1),
+                     "gemm_share_of_step": (gemm_ms / 1e3) / secs,
+                     "traffic": GEMM_DRAM_BYTES_PER_LAUNCH},
+    }
+    if not args.no_cpu_baseline:
+        cstep, cflops, desc = cpu_sample_step(H, F, rows // E)
+        ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)
+        line["cpu_baseline"] = {"value": ctf, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                "sample": desc}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = args.workload
+    if workload == "auto":
+        workload = "mixtral" if max(world, args.gpus) == 1 else "ep"
+    if args.impl == "reference":
+        if workload == "mixtral":
+            wl = mixtral_workload()
+            reference_arm(args, wl["name"], wl["H"], wl["F"], wl["rows"] // wl["E"])
+        else:
+            from fp8_gmm_b200 import ep_bench
+
+            reference_arm(args, ep_bench.WORKLOAD_NAME, ep_bench.H, ep_bench.F, ep_bench.ROWS_PER_EXPERT)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: fp8_gmm_b200 has no CPU path (use --impl reference for the CPU baseline)")
+    if workload == "mixtral":
+        run_single(args)
+    else:
+        from fp8_gmm_b200 import ep_bench
+
+        ep_bench.run(args, METRIC, measured_peaks(), ClockSampler, cpu_sample_step, run_cpu)
+
+
+if __name__ == "__main__":
+    main()

@@ -65,6 +65,7 @@ SYMBOLS = {
     "fp8gmm_version": (ctypes.c_int, []),
     "fp8gmm_last_error": (ctypes.c_char_p, []),
     "fp8gmm_device_status": (ctypes.c_int, [c_vp]),
+    "fp8gmm_launch_count": (ctypes.c_uint64, []),
     "fp8gmm_multi_quantize": (ctypes.c_int, [ctypes.POINTER(TensorDesc), ctypes.c_int, ctypes.c_int, c_vp]),
     "fp8gmm_multi_pad_transpose": (ctypes.c_int, [ctypes.POINTER(TensorDesc), ctypes.c_int, c_vp]),
     "fp8gmm_multi_pad_cast_transpose": (ctypes.c_int, [ctypes.POINTER(TensorDesc), ctypes.c_int, ctypes.c_int, c_vp]),
@@ -83,13 +84,19 @@ SYMBOLS = {
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m fp8_gmm_b200.csrc.build` (needs nvcc). "
+        f"{LIB_PATH} is missing: build it with `python fp8_gmm_b200/csrc/build.py` (needs nvcc). "
         "fp8_gmm_b200 has no CPU or PyTorch fallback."
     )
 
 lib = ctypes.CDLL(LIB_PATH)
 for _name, (_res, _args) in SYMBOLS.items():
-    _fn = getattr(lib, _name)
+    try:
+        _fn = getattr(lib, _name)
+    except AttributeError as exc:
+        raise ImportError(
+            f"{LIB_PATH} does not export {_name}: it is older than the sources; rebuild it with "
+            "`python fp8_gmm_b200/csrc/build.py`"
+        ) from exc
     _fn.restype = _res
     _fn.argtypes = _args
 

@@ -26,6 +26,38 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+# Optional per-launch timing of the GEMM kernel (used by bench.py for its roofline line): when a list is
+# installed, every GEMM call appends (start_event, end_event, flops) recorded on the launching stream.
+_gemm_timings = None
+
+
+def set_gemm_timings(sink):
+    """Install (or with None remove) a list that receives (start, end, flops) per GEMM launch."""
+    global _gemm_timings
+    _gemm_timings = sink
+
+
+def launch_count():
+    """Kernels launched by the C-ABI library in this process so far."""
+    return int(lib.fp8gmm_launch_count())
+
+
+class _Timed:
+    def __init__(self, flops):
+        self.flops = flops
+
+    def __enter__(self):
+        if _gemm_timings is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+
+    def __exit__(self, *exc):
+        if _gemm_timings is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            _gemm_timings.append((self.start, end, self.flops))
+
+
 def _require(cond, msg):
     if not cond:
         raise RuntimeError(msg)
@@ -269,7 +301,8 @@ def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax):
     args.act_out = _ptr(act_out)
     args.act_scale, args.act_scale_stride = sc.ptr, sc.stride
     args.act_amax, args.act_amax_stride = amax.ptr, amax.stride
-    check(lib.fp8gmm_grouped_gemm(ctypes.byref(args), _stream()), "fp8_gmm")
+    with _Timed(2.0 * a.shape[0] * args.n * args.k):
+        check(lib.fp8gmm_grouped_gemm(ctypes.byref(args), _stream()), "fp8_gmm")
     if amax.scatter:
         amax.scatter()
     del keep
@@ -398,7 +431,8 @@ def grouped_wgrad(a_t, b_t, t_offsets, n, k, a_scale_invs, b_scale_invs, c=None)
     nbytes = lib.fp8gmm_wgrad_workspace_bytes(G)
     ws = _workspace(a_t.device, nbytes)
     args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
-    check(lib.fp8gmm_grouped_wgrad(ctypes.byref(args), _stream()), "grouped_wgrad")
+    with _Timed(2.0 * a_t.numel() * k):  # a_t holds (padded rows) x n elements
+        check(lib.fp8gmm_grouped_wgrad(ctypes.byref(args), _stream()), "grouped_wgrad")
     del keep
     return c
 

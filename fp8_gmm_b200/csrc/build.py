@@ -1,6 +1,7 @@
 """Build libfp8gmm_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-Usage: python -m fp8_gmm_b200.csrc.build [--force] [--verbose]
+Usage: python fp8_gmm_b200/csrc/build.py [--force] [--verbose]   (run as a script: it must not import the
+package, whose import needs the library this script produces)
 
 The library has no Python, torch or pybind dependency: it is plain CUDA C++ linked against the static
 CUDA runtime, and is loaded from Python with ctypes (fp8_gmm_b200/_lib.py).  nvcc cross-compiles

@@ -17,6 +17,7 @@ void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t err, const char* what);
 int sm_count();              // SMs of the current device (cached per device)
 int* device_status_word();   // device address of the per-device status word (kernels report timeouts here)
+void count_launch();         // bumps the process-wide launch counter (fp8gmm_launch_count)
 
 #define FP8GMM_CHECK_ARG(cond, ...)       \
   do {                                    \

@@ -568,6 +568,7 @@ int launch(const GemmParams& p, cudaStream_t s) {
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, s>>>(p);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
+  count_launch();
   return FP8GMM_OK;
 }
 

@@ -259,6 +259,7 @@ int launch_mode(const PadArgs& args, int out_format, cudaStream_t s) {
   else
     multi_pad_kernel<kMode, FP8GMM_E5M2><<<grid, kThreads, 0, s>>>(args);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
+  count_launch();
   return FP8GMM_OK;
 }
 

@@ -178,6 +178,7 @@ int fp8gmm_multi_quantize(const fp8gmm_tensor_desc* descs, int count, int out_fo
     else
       multi_quantize_kernel<FP8GMM_E5M2><<<grid, kThreads, 0, s>>>(args);
     FP8GMM_CHECK_CUDA(cudaGetLastError());
+    count_launch();
   }
   return FP8GMM_OK;
 }
@@ -212,6 +213,7 @@ int fp8gmm_multi_scale_mul(const fp8gmm_scale_mul_desc* descs, int count, void* 
     }
     multi_scale_mul_kernel<<<args.tile_start[args.num], kThreads, 0, s>>>(args);
     FP8GMM_CHECK_CUDA(cudaGetLastError());
+    count_launch();
   }
   return FP8GMM_OK;
 }

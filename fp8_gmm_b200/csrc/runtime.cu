@@ -1,5 +1,6 @@
 // Host-side plumbing of the C ABI: error strings, device queries, the per-device status word that
 // kernels use to report a bounded wait that ran out, and the delayed-scaling recipe update kernel.
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <mutex>
@@ -14,6 +15,7 @@ constexpr int kMaxDevices = 64;
 int g_sm_count[kMaxDevices] = {0};
 int* g_status_addr[kMaxDevices] = {nullptr};
 std::mutex g_mutex;
+std::atomic<uint64_t> g_launches{0};
 
 // One status word per device that loads the library (a __device__ variable is instantiated per device).
 __device__ int g_device_status = 0;
@@ -36,6 +38,8 @@ static int current_device() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
   return dev;
 }
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {
   const int dev = current_device();
@@ -97,6 +101,8 @@ extern "C" {
 
 int fp8gmm_version(void) { return 1000; }
 
+uint64_t fp8gmm_launch_count(void) { return fp8gmm::g_launches.load(std::memory_order_relaxed); }
+
 const char* fp8gmm_last_error(void) { return fp8gmm::g_error; }
 
 int fp8gmm_device_status(void* stream) {
@@ -128,6 +134,7 @@ int fp8gmm_delayed_scaling_update(float* amax_history, float* scale, float* scal
   fp8gmm::delayed_scaling_update_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       amax_history, scale, scale_inv, history_len, n, fp8_max, inv_pow2, algo);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
+  fp8gmm::count_launch();
   return FP8GMM_OK;
 }
 

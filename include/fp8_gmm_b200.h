@@ -53,6 +53,12 @@ const char* fp8gmm_last_error(void);
  */
 int fp8gmm_device_status(void* stream);
 
+/*
+ * Number of kernels this library has launched in this process so far (all devices, all threads).
+ * Benchmarks difference it around a timed region to state how much of the work ran in these kernels.
+ */
+uint64_t fp8gmm_launch_count(void);
+
 /* ------------------------------------------------------------------------------------------------
  * Multi-tensor elementwise kernels (HBM-bound).
  *

@@ -199,7 +199,8 @@ def delayed_scaling_update(amax_history, scale, fp8_max, margin=0, algo="max"):
     """amax = max over history (or most recent); scale = fp8_max / amax / 2^margin where amax is
     positive and finite, else unchanged; scale_inv = 1/scale; history rolled by one with row 0 zeroed."""
     amax = amax_history.max(dim=0).values if algo == "max" else amax_history[0].clone()
-    sf = (fp8_max / amax) / (2.0**margin)
+    # IEEE division (torch's `scalar / tensor` would multiply by a rounded reciprocal instead)
+    sf = torch.full_like(amax, fp8_max) / amax / (2.0**margin)
     sf = torch.where(amax > 0.0, sf, scale)
     sf = torch.where(torch.isfinite(amax), sf, scale)
     if amax_history.shape[0] > 1:

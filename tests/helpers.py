@@ -34,3 +34,15 @@ def routed_group_sizes(num_groups, rows, seed, zipf_s=None):
         p = (p / p.sum()).float()
     idx = torch.multinomial(p, rows, replacement=True, generator=g)
     return torch.bincount(idx, minlength=num_groups).tolist()
+
+
+def fp8_steps(a, b):
+    """Distance in representable FP8 steps between two byte tensors (sign-magnitude order, -0 == +0).
+
+    The activation-fused kernels can produce a zero of either sign where the CPU evaluates the
+    activation derivative to a zero of the other sign; as numbers they are identical."""
+    def ordered(t):
+        t = t.contiguous().view(torch.uint8).int()
+        mag = t & 0x7F
+        return torch.where(t >= 0x80, -mag, mag)
+    return (ordered(a) - ordered(b)).abs()
