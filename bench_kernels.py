@@ -1,0 +1,198 @@
+"""Per-kernel microbenchmarks (CUDA-event timed) for the three kernel families of fp8_gmm_b200.
+
+    python bench_kernels.py gemm  [--groups G --rows R --n N --k K --act none|gelu|swiglu --a-format e4m3|e5m2]
+    python bench_kernels.py wgrad [--groups G --rows R --n N --k K]
+    python bench_kernels.py step-gemms            # the six GEMMs of the Mixtral-shaped step, one by one
+    python bench_kernels.py pad   [--groups G --max-rows M --cols K --mode cast|amax+cast|transpose|quantize]
+                                                  # default = the pad-fusion microbenchmark: 256 groups, rows ~ U[0,4096],
+                                                  # K = 7168, bf16 ~ N(0,3) with 0.1 % outliers x100
+    common: [--iters I --warmup W]
+
+Every sub-command prints one JSON line.  GEMMs report TFLOP/s (algorithmic FLOPs, true rows) and the
+fraction of 2 x the measured dense bf16 rate; the HBM-bound kernels report GB/s (algorithmic bytes:
+cast + padded transpose = 2mn read + mn + Mpad*n written; quantise = 3 bytes per element; fp8 transpose =
+mn + Mpad*n) and the fraction of the measured copy bandwidth and of the nominal 8 TB/s.  Working sets
+exceed the 126 MB L2 in the default configurations.  These are also the small cases used for ncu captures.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_ms(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def rand_fp8(shape, dtype, dev, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    b = torch.randint(0, 256, shape, generator=g, dtype=torch.uint8, device=dev)
+    b = torch.where((b & 0x7F) >= 0x70, b & 0x8F | 0x30, b)  # moderate magnitudes, no NaN/Inf encodings
+    return b.view(dtype)
+
+
+def even_sizes(groups, rows):
+    base = rows // groups
+    sizes = [base] * groups
+    sizes[-1] += rows - base * groups
+    return sizes
+
+
+def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label):
+    G, m = len(sizes), sum(sizes)
+    a = rand_fp8((m, k), a_dtype, dev, 1)
+    b = rand_fp8((G, n, k), E4, dev, 2)
+    ones = torch.ones(G, device=dev)
+    ms_sizes = torch.tensor(sizes)
+    if act == "none":
+        c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: backend.fp8_gmm(a, b, ms_sizes, ones, ones, c=c)  # noqa: E731
+    else:
+        n_act = n // 2 if act == "swiglu" else n
+        pre = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        c = torch.empty(m, n_act, dtype=E4, device=dev)
+        amax = torch.zeros(G, device=dev)
+        fn = lambda: backend.fp8_gmm(a, b, ms_sizes, ones, ones, c=c, pre_gelu_out=pre, c_scales=ones, c_amaxes=amax,  # noqa: E731
+                                     activation=act)
+    ms = time_ms(fn, iters, warmup)
+    backend.device_status()
+    _, bf16, src = peaks()
+    tf = 2.0 * m * n * k / ms / 1e9
+    return {"kernel": "grouped_gemm", "case": label, "groups": G, "rows": m, "n": n, "k": k, "act": act,
+            "a_format": "e4m3" if a_dtype == E4 else "e5m2", "ms": ms, "tflops": tf,
+            "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
+
+
+def wgrad_case(backend, dev, sizes, n, k, iters, warmup, label):
+    from fp8_gmm_b200.utils import cumsum_group_sizes
+
+    G, padded, cums, pcs = cumsum_group_sizes(sizes, need_padding=True)
+    offs = pcs if padded else cums
+    a_t = rand_fp8((offs[-1] * n,), E5, dev, 3)
+    b_t = rand_fp8((offs[-1] * k,), E4, dev, 4)
+    ones = torch.ones(G, device=dev)
+    c = torch.empty(G, n, k, dtype=torch.bfloat16, device=dev)
+    fn = lambda: backend.grouped_wgrad(a_t, b_t, offs, n, k, ones, ones, c=c)  # noqa: E731
+    ms = time_ms(fn, iters, warmup)
+    backend.device_status()
+    _, bf16, src = peaks()
+    tf = 2.0 * sum(sizes) * n * k / ms / 1e9
+    return {"kernel": "grouped_gemm(wgrad)", "case": label, "groups": G, "rows": sum(sizes), "n": n, "k": k, "ms": ms,
+            "tflops": tf, "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
+
+
+def pad_case(backend, dev, args):
+    g = torch.Generator().manual_seed(0)
+    rows = torch.randint(0, args.max_rows + 1, (args.groups,), generator=g).tolist()
+    from fp8_gmm_b200.utils import cumsum_group_sizes
+
+    G, padded, cums, pcs = cumsum_group_sizes(rows, need_padding=True)
+    m, k = cums[-1], args.cols
+    gd = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(m, k, generator=gd, device=dev) * 3.0
+    x = torch.where(torch.rand(m, k, generator=gd, device=dev) < 1e-3, x * 100.0, x).to(torch.bfloat16)
+    out = torch.empty(m, k, dtype=E4, device=dev)
+    out_t = torch.empty(pcs[-1], k, dtype=E4, device=dev)
+    scale = torch.ones(G, device=dev)
+    amax = torch.zeros(G, device=dev)
+    hbm, _, src = peaks()
+    if args.mode == "cast":
+        fn = lambda: backend.grouped_cast_transpose(x, cums, out, out_t, pcs, (scale, 1), (amax, 1))  # noqa: E731
+        nbytes = 2 * m * k + m * k + pcs[-1] * k
+    elif args.mode == "amax+cast":
+        views = [x[cums[i]:cums[i + 1]] for i in range(G)]
+        am = [amax[i] for i in range(G)]
+
+        def fn():
+            amax.zero_()
+            backend.multi_amax(views, am)
+            torch.div(448.0, torch.clamp(amax, min=1e-30), out=scale)
+            backend.grouped_cast_transpose(x, cums, out, out_t, pcs, (scale, 1), None)
+
+        nbytes = 2 * m * k + 2 * m * k + m * k + pcs[-1] * k
+    elif args.mode == "transpose":
+        fn = lambda: backend.grouped_cast_transpose(out, cums, None, out_t, pcs, None, None)  # noqa: E731
+        nbytes = m * k + pcs[-1] * k
+    else:
+        views = [x[cums[i]:cums[i + 1]] for i in range(G)]
+        outs = [out[cums[i]:cums[i + 1]] for i in range(G)]
+        sc, am = [scale[i] for i in range(G)], [amax[i] for i in range(G)]
+        fn = lambda: backend.multi_quantize(views, outs, sc, am)  # noqa: E731
+        nbytes = 3 * m * k
+    ms = time_ms(fn, args.iters, args.warmup)
+    gbs = nbytes / ms / 1e6
+    return {"kernel": "multi_pad/" + args.mode, "groups": G, "rows": m, "padded_rows": pcs[-1], "cols": k, "ms": ms,
+            "algorithmic_bytes": nbytes, "GBps": gbs, "frac_of_hbm_" + src: gbs / hbm, "frac_of_nominal_8000": gbs / 8000.0}
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("what", choices=["gemm", "wgrad", "step-gemms", "pad"])
+    p.add_argument("--groups", type=int, default=None)
+    p.add_argument("--rows", type=int, default=32768)
+    p.add_argument("--n", type=int, default=4096)
+    p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--act", default="none", choices=["none", "gelu", "swiglu"])
+    p.add_argument("--a-format", default="e4m3", choices=["e4m3", "e5m2"])
+    p.add_argument("--max-rows", type=int, default=4096)
+    p.add_argument("--cols", type=int, default=7168)
+    p.add_argument("--mode", default="cast", choices=["cast", "amax+cast", "transpose", "quantize"])
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    args = p.parse_args()
+    from fp8_gmm_b200 import backend
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    if args.what == "gemm":
+        sizes = even_sizes(args.groups or 8, args.rows)
+        print(json.dumps(gemm_case(backend, dev, sizes, args.n, args.k, args.act, E4 if args.a_format == "e4m3" else E5,
+                                   args.iters, args.warmup, "custom")))
+    elif args.what == "wgrad":
+        sizes = even_sizes(args.groups or 8, args.rows)
+        print(json.dumps(wgrad_case(backend, dev, sizes, args.n, args.k, args.iters, args.warmup, "custom")))
+    elif args.what == "step-gemms":
+        sizes, H, F = even_sizes(8, 32768), 4096, 14336
+        for label, fn in [
+            ("fc1 fwd + SwiGLU epilogue", lambda: gemm_case(backend, dev, sizes, 2 * F, H, "swiglu", E4, args.iters, args.warmup, "fc1_fwd")),
+            ("fc2 fwd", lambda: gemm_case(backend, dev, sizes, H, F, "none", E4, args.iters, args.warmup, "fc2_fwd")),
+            ("fc2 dgrad", lambda: gemm_case(backend, dev, sizes, F, H, "none", E5, args.iters, args.warmup, "fc2_dgrad")),
+            ("fc1 dgrad", lambda: gemm_case(backend, dev, sizes, H, 2 * F, "none", E5, args.iters, args.warmup, "fc1_dgrad")),
+            ("fc2 wgrad", lambda: wgrad_case(backend, dev, sizes, H, F, args.iters, args.warmup, "fc2_wgrad")),
+            ("fc1 wgrad", lambda: wgrad_case(backend, dev, sizes, 2 * F, H, args.iters, args.warmup, "fc1_wgrad")),
+        ]:
+            print(json.dumps(fn()), flush=True)
+            torch.cuda.empty_cache()
+    else:
+        if args.groups is None:
+            args.groups = 256
+        print(json.dumps(pad_case(backend, dev, args)))
+
+
+if __name__ == "__main__":
+    main()

@@ -170,6 +170,7 @@ def test_state_dict_round_trip_reproduces_fp8_state(cuda):
     outs = []
     for layer in (a, b):
         xin = x.clone().requires_grad_(True)
+        layer.weight_tensor.grad = None
         with fg.fp8_autocast(enabled=True, fp8_recipe=rec):
             y = layer(xin, torch.tensor(sizes))
         y.sum().backward()
