@@ -36,16 +36,25 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+LAST_CLOCKS = None
+
+
 def time_ms(fn, iters, warmup):
+    """Mean milliseconds per call over `iters` back-to-back calls; SM clocks are sampled meanwhile."""
+    global LAST_CLOCKS
+    from bench import ClockSampler
+
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(iters):
-        fn()
-    e.record()
-    torch.cuda.synchronize()
+    with ClockSampler(0) as clocks:
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+    LAST_CLOCKS = clocks.summary()
     return s.elapsed_time(e) / iters
 
 
@@ -81,11 +90,34 @@ def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label):
                                      activation=act)
     ms = time_ms(fn, iters, warmup)
     backend.device_status()
+    stalls = gemm_stall_profile(backend, fn) if os.environ.get("FP8GMM_BENCH_STALLS") else None
     _, bf16, src = peaks()
     tf = 2.0 * m * n * k / ms / 1e9
-    return {"kernel": "grouped_gemm", "case": label, "groups": G, "rows": m, "n": n, "k": k, "act": act,
-            "a_format": "e4m3" if a_dtype == E4 else "e5m2", "ms": ms, "tflops": tf,
+    return {"kernel": "grouped_gemm", "case": label, "stalls": stalls, "groups": G, "rows": m, "n": n, "k": k, "act": act,
+            "a_format": "e4m3" if a_dtype == E4 else "e5m2", "ms": ms, "tflops": tf, "clocks": LAST_CLOCKS,
             "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
+
+
+def gemm_stall_profile(backend, fn):
+    """One extra launch with the library's stall counters on: mean cycles per CTA (FP8GMM_BENCH_STALLS=1)."""
+    from fp8_gmm_b200._lib import lib
+
+    buf = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
+    lib.fp8gmm_set_gemm_profile_buffer(buf.data_ptr(), buf.numel() * 8)
+    fn()
+    torch.cuda.synchronize()
+    lib.fp8gmm_set_gemm_profile_buffer(None, 0)
+    t = buf.view(148, 8).double()
+    active = t[t[:, 5] > 0]
+    lead = t[t[:, 3] > 0]
+    names = ["producer_wait_stage", "mma_wait_operands", "mma_wait_accumulator", "mma_total", "epilogue_wait", "epilogue_busy",
+             "mma_issue", "mma_total_ns"]
+    out = {}
+    for i, nm in enumerate(names):
+        src = lead if i in (1, 2, 3, 6, 7) else active
+        out[nm] = float(src[:, i].mean()) if src.numel() else 0.0
+    out["sm_ghz"] = out["mma_total"] / out["mma_total_ns"] if out["mma_total_ns"] else None
+    return out
 
 
 def wgrad_case(backend, dev, sizes, n, k, iters, warmup, label):
@@ -103,7 +135,7 @@ def wgrad_case(backend, dev, sizes, n, k, iters, warmup, label):
     _, bf16, src = peaks()
     tf = 2.0 * sum(sizes) * n * k / ms / 1e9
     return {"kernel": "grouped_gemm(wgrad)", "case": label, "groups": G, "rows": sum(sizes), "n": n, "k": k, "ms": ms,
-            "tflops": tf, "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
+            "tflops": tf, "clocks": LAST_CLOCKS, "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
 
 
 def pad_case(backend, dev, args):
@@ -146,7 +178,7 @@ def pad_case(backend, dev, args):
         nbytes = 3 * m * k
     ms = time_ms(fn, args.iters, args.warmup)
     gbs = nbytes / ms / 1e6
-    return {"kernel": "multi_pad/" + args.mode, "groups": G, "rows": m, "padded_rows": pcs[-1], "cols": k, "ms": ms,
+    return {"kernel": "multi_pad/" + args.mode, "clocks": LAST_CLOCKS, "groups": G, "rows": m, "padded_rows": pcs[-1], "cols": k, "ms": ms,
             "algorithmic_bytes": nbytes, "GBps": gbs, "frac_of_hbm_" + src: gbs / hbm, "frac_of_nominal_8000": gbs / 8000.0}
 
 

@@ -29,6 +29,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -40,15 +41,12 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;  // bytes == fp8 elements
-constexpr int kStages = 4;
 constexpr int kSuperRows = 32;  // m-tiles per super-row of the tile order
 constexpr int kThreads = 192;
 constexpr int kTileABytes = kBlockM * kBlockK;          // 16 KiB
 constexpr int kTileBBytes = kBlockN * kBlockK;          // 32 KiB
-constexpr int kStageBytes = kTileABytes + kTileBBytes;  // 48 KiB
 constexpr int kTmemCols = 512;
 constexpr int kMaxGroups = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 enum GemmMode { kModeRows = 0, kModeWgrad = 1 };
@@ -67,6 +65,8 @@ struct GemmParams {
   int64_t ldc;     // row pitch of c in elements
   int64_t ld_act;  // row pitch of act_out in bytes
   int* status;
+  long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
+  int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
   int mode;
   int activation;
   int num_groups;
@@ -137,6 +137,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -203,12 +207,17 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 struct TileInfo {
   int group, mt, nt;
   int num_kb;      // K blocks of 128 bytes
-  int valid_rows;  // rows of this tile that belong to the output
+  int valid_rows;  // rows of this CTA's 128-row slab that belong to the output (may be <= 0)
   int valid_cols;
-  int64_t row0;    // first output row (kModeRows: global row; kModeWgrad: row inside C_g)
+  int64_t row0;    // first output row of this CTA's slab (kModeRows: global row; kModeWgrad: row inside C_g)
 };
 
-__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
+// kCtas = 1: a CTA owns a 128 x 256 tile.  kCtas = 2: a pair of CTAs (cluster of 2) owns a 256 x 256
+// tile, CTA `rank` holding rows [128*rank, 128*rank+128) of it.
+template <int kCtas>
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile, int rank) {
+  constexpr int kTileM = kBlockM * kCtas;
+  constexpr int kSuper = kSuperRows / kCtas;
   TileInfo t;
   const int g = upper_slot(p.tile_start, p.num_groups, tile);
   const int local = tile - p.tile_start[g];
@@ -220,33 +229,98 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
     rows_g = p.m_fixed;
     contraction = p.row_start[g + 1] - p.row_start[g];
   }
-  const int mt_g = (rows_g + kBlockM - 1) / kBlockM;
-  const int per_super = kSuperRows * p.tiles_n;
+  const int mt_g = (rows_g + kTileM - 1) / kTileM;
+  const int per_super = kSuper * p.tiles_n;
   const int s = local / per_super;
   const int rem = local - s * per_super;
-  const int h = min(kSuperRows, mt_g - s * kSuperRows);
+  const int h = min(kSuper, mt_g - s * kSuper);
   t.group = g;
   t.nt = rem / h;
-  t.mt = s * kSuperRows + rem % h;
+  t.mt = s * kSuper + rem % h;
   t.num_kb = (contraction + kBlockK - 1) / kBlockK;
-  t.valid_rows = min(kBlockM, rows_g - t.mt * kBlockM);
+  const int slab = t.mt * kTileM + rank * kBlockM;
+  t.valid_rows = min(kBlockM, rows_g - slab);
   const int tile_n = p.activation == FP8GMM_ACT_SWIGLU ? kBlockN / 2 : kBlockN;
   const int n_cols = p.activation == FP8GMM_ACT_SWIGLU ? p.n / 2 : p.n;
   t.valid_cols = min(tile_n, n_cols - t.nt * tile_n);
-  t.row0 = (p.mode == kModeRows ? static_cast<int64_t>(p.row_start[g]) : 0) + static_cast<int64_t>(t.mt) * kBlockM;
+  t.row0 = (p.mode == kModeRows ? static_cast<int64_t>(p.row_start[g]) : 0) + slab;
   return t;
 }
+
+// ---- cluster helpers (kCtas = 2) ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes may be credited to an mbarrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// One MMA over both CTAs of the pair: M = 256 (128 rows from each CTA's A tile and TMEM), N = 256 (128 B rows
+// from each CTA's shared memory); issued by one thread of the leader CTA.
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in both CTAs once all MMAs issued so far are complete.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+
+template <int kCtas>
+struct Cfg {
+  static constexpr int kStages = kCtas == 1 ? 4 : 6;
+  static constexpr int kBRows = kBlockN / kCtas;              // B rows held by one CTA
+  static constexpr int kBBytes = kBRows * kBlockK;
+  static constexpr int kStageBytes = kTileABytes + kBBytes;   // 48 KiB (1 CTA) / 32 KiB (pair)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+template <int kCtas>
+__device__ __forceinline__ void gemm_body(const GemmParams& p) {
+  using C = Cfg<kCtas>;
+  constexpr int kStages = C::kStages;
+  constexpr int kStageBytes = C::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;  // SWIZZLE_128B atoms need 1024-byte alignment
   uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + kStages * kStageBytes);
-  // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
@@ -256,6 +330,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = kCtas == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+  const bool leader = rank == 0;
+  const int worker = kCtas == 2 ? blockIdx.x >> 1 : blockIdx.x;        // tile-sequence index of this CTA (pair)
+  const int num_workers = kCtas == 2 ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -264,109 +342,161 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 4 * kCtas);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_base_slot), kTmemCols);
-    tmem_relinquish();
+    if (kCtas == 2) {
+      tmem_alloc_pair(smem_u32(tmem_base_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_base_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (kCtas == 2) cluster_sync_all(); else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
   if (warp == 0) {
-    // ===================== TMA producer =====================
-    if (lane == 0 && p.mode == kModeRows) {
-      prefetch_tensormap(&p.map_a);
-      prefetch_tensormap(&p.map_b);
-    }
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-      const TileInfo t = decode_tile(p, tile);
-      const CUtensorMap* map_a = p.mode == kModeRows ? &p.map_a : &p.maps[2 * t.group];
-      const CUtensorMap* map_b = p.mode == kModeRows ? &p.map_b : &p.maps[2 * t.group + 1];
-      int ya, yb0, yb1;
+    // ===================== TMA producer (every CTA loads its own operand slabs) =====================
+    // One thread runs the whole loop; the other lanes park at the __syncwarp below.
+    if (lane == 0) {
       if (p.mode == kModeRows) {
-        ya = static_cast<int>(t.row0);
+        prefetch_tensormap(&p.map_a);
+        prefetch_tensormap(&p.map_b);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long wait_empty = 0;
+      const uint32_t full0_leader = kCtas == 2 ? map_to_cta(full_bar(0), 0) : 0;
+      for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
+        const TileInfo t = decode_tile<kCtas>(p, tile, rank);
+        const CUtensorMap* map_a = p.mode == kModeRows ? &p.map_a : &p.maps[2 * t.group];
+        const CUtensorMap* map_b = p.mode == kModeRows ? &p.map_b : &p.maps[2 * t.group + 1];
+        // first B row of each 128-row box this CTA loads: 1 CTA -> two boxes (columns [0,128) and [128,256) of the
+        // tile); pair -> one box, the half selected by `rank`.  SwiGLU: first half = gate rows, second = up rows.
+        int yb0, yb1;
+        const int b_base = p.mode == kModeRows ? t.group * p.n : 0;
         if (p.activation == FP8GMM_ACT_SWIGLU) {
-          yb0 = t.group * p.n + t.nt * (kBlockN / 2);  // gate rows
-          yb1 = yb0 + p.n / 2;                         // matching up rows
+          yb0 = b_base + t.nt * (kBlockN / 2);
+          yb1 = yb0 + p.n / 2;
         } else {
-          yb0 = t.group * p.n + t.nt * kBlockN;
+          yb0 = b_base + t.nt * kBlockN;
           yb1 = yb0 + kBlockN / 2;
         }
-      } else {
-        ya = t.mt * kBlockM;
-        yb0 = t.nt * kBlockN;
-        yb1 = yb0 + kBlockN / 2;
-      }
-      for (int kb = 0; kb < t.num_kb && ok; ++kb) {
-        if (lane == 0) {
+        const int ya = static_cast<int>(t.row0);
+        const int yb_mine = rank == 0 ? yb0 : yb1;
+        for (int kb = 0; kb < t.num_kb && ok; ++kb) {
+          if (p.prefetch_kb > 0 && kb + p.prefetch_kb < t.num_kb) {
+            // warm L2 for a K block that the ring will only reach later, so its load sees L2 latency, not DRAM's
+            const int xp = (kb + p.prefetch_kb) * kBlockK;
+            prefetch_l2_2d(map_a, xp, ya);
+            if (kCtas == 1) {
+              prefetch_l2_2d(map_b, xp, yb0);
+              prefetch_l2_2d(map_b, xp, yb1);
+            } else {
+              prefetch_l2_2d(map_b, xp, yb_mine);
+            }
+          }
+          const long long t0 = p.profile ? clock64() : 0;
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x1);
+          if (p.profile) wait_empty += clock64() - t0;
           if (ok) {
             const uint32_t sa = tiles_addr + stage * kStageBytes;
             const uint32_t sb = sa + kTileABytes;
-            mbar_expect_tx(full_bar(stage), kStageBytes);
-            tma_load_2d(sa, map_a, full_bar(stage), kb * kBlockK, ya);
-            tma_load_2d(sb, map_b, full_bar(stage), kb * kBlockK, yb0);
-            tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), kb * kBlockK, yb1);
-          }
-        }
-        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ===================== MMA issuer =====================
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-      const TileInfo t = decode_tile(p, tile);
-      if (t.num_kb == 0) continue;  // empty contraction: the epilogue writes zeros on its own
-      if (lane == 0) ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x2);
-      ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
-      for (int kb = 0; kb < t.num_kb && ok; ++kb) {
-        if (lane == 0) {
-          ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, 0x4);
-          if (ok) {
-            tc_fence_after();
-            const uint32_t sa = tiles_addr + stage * kStageBytes;
-            const uint64_t da = make_smem_desc(sa);
-            const uint64_t db = make_smem_desc(sa + kTileABytes);
-#pragma unroll
-            for (int k = 0; k < kBlockK / 32; ++k) {
-              // advance both descriptors by 32 bytes (>>4 = 2) along K inside the swizzle atom
-              umma_f8(tmem_d, da + 2ull * k, db + 2ull * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            if (kCtas == 1) {
+              mbar_expect_tx(full_bar(stage), kStageBytes);
+              tma_load_2d(sa, map_a, full_bar(stage), kb * kBlockK, ya);
+              tma_load_2d(sb, map_b, full_bar(stage), kb * kBlockK, yb0);
+              tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), kb * kBlockK, yb1);
+            } else {
+              // both CTAs credit the leader's barrier; the leader arms it for the bytes of both
+              const uint32_t bar = full0_leader + 8u * stage;
+              if (leader) mbar_expect_tx(full_bar(stage), 2 * kStageBytes);
+              tma_load_2d_pair(sa, map_a, bar, kb * kBlockK, ya);
+              tma_load_2d_pair(sb, map_b, bar, kb * kBlockK, yb_mine);
             }
-            umma_commit(empty_bar(stage));
-            if (kb == t.num_kb - 1) umma_commit(tfull_bar(acc));
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
-        ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
       }
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      if (p.profile) p.profile[blockIdx.x * 8 + 0] = wait_empty;
     }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer: one thread (of the leader CTA when paired) =====================
+    // The loop is latency critical -- it has to stay ahead of a tensor pipe that retires one K block every
+    // 512 cycles -- so it runs in a single thread without warp-level synchronisation inside.
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      long long wait_full = 0, wait_tempty = 0, issue = 0;
+      const long long t_begin = p.profile ? clock64() : 0;
+      const unsigned long long ns_begin = p.profile ? global_ns() : 0;
+      const uint64_t desc_a0 = make_smem_desc(tiles_addr);
+      const uint64_t desc_b0 = make_smem_desc(tiles_addr + kTileABytes);
+      const uint32_t idesc = p.idesc;
+      for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
+        const TileInfo t = decode_tile<kCtas>(p, tile, rank);
+        if (t.num_kb == 0) continue;  // empty contraction: the epilogue writes zeros on its own
+        const long long t0 = p.profile ? clock64() : 0;
+        ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x2);
+        if (p.profile) wait_tempty += clock64() - t0;
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
+        for (int kb = 0; kb < t.num_kb; ++kb) {
+          const long long t1 = p.profile ? clock64() : 0;
+          ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, 0x4);
+          if (!ok) break;
+          const long long t2 = p.profile ? clock64() : 0;
+          // descriptors of this stage: the start-address field counts 16-byte units
+          const uint64_t da = desc_a0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
+          const uint64_t db = desc_b0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
+#pragma unroll
+          for (int k = 0; k < kBlockK / 32; ++k) {
+            // advance both descriptors by 32 bytes (>>4 = 2) along K inside the swizzle atom
+            if (kCtas == 1)
+              umma_f8(tmem_d, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f8_pair(tmem_d, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          if (kCtas == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage));
+          if (p.profile) {
+            wait_full += t2 - t1;
+            issue += clock64() - t2;
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (kCtas == 1) umma_commit(tfull_bar(acc)); else umma_commit_pair(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (p.profile) {
+        p.profile[blockIdx.x * 8 + 1] = wait_full;
+        p.profile[blockIdx.x * 8 + 2] = wait_tempty;
+        p.profile[blockIdx.x * 8 + 3] = clock64() - t_begin;
+        p.profile[blockIdx.x * 8 + 6] = issue;
+        p.profile[blockIdx.x * 8 + 7] = static_cast<long long>(global_ns() - ns_begin);
+      }
+    }
+    __syncwarp();
   } else {
     // ===================== epilogue (warps 2..5) =====================
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
@@ -374,8 +504,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-      const TileInfo t = decode_tile(p, tile);
+    long long wait_tfull = 0, busy = 0;
+    for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
+      const TileInfo t = decode_tile<kCtas>(p, tile, rank);
       const bool row_ok = row_in_tile < t.valid_rows;
       const int64_t out_row = t.row0 + row_in_tile;
       const float alpha = p.sa[t.group * p.sa_stride] * p.sb[t.group * p.sb_stride];
@@ -387,9 +518,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
         }
         continue;
       }
+      const long long t0 = p.profile ? clock64() : 0;
       if (lane == 0) ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x8);
       ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
       if (!ok) break;
+      const long long t1 = p.profile ? clock64() : 0;
+      wait_tfull += t1 - t0;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quad * 32) << 16);
 
@@ -487,30 +621,43 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_
           if (lane == 0) atomic_max_nonneg(p.amax + t.group * p.amax_stride, amax);
         }
       }
-      // hand the accumulator back to the MMA warp
+      // hand the accumulator back to the MMA warp (which lives in the leader CTA when paired)
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (kCtas == 1) mbar_arrive(tempty_bar(acc)); else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+      }
+      if (p.profile) busy += clock64() - t1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (p.profile && warp == 2 && lane == 0) {
+      p.profile[blockIdx.x * 8 + 4] = wait_tfull;
+      p.profile[blockIdx.x * 8 + 5] = busy;
     }
   }
 
   // ===================== teardown =====================
   tc_fence_before();
-  __syncthreads();
+  if (kCtas == 2) cluster_sync_all(); else __syncthreads();
   if (*abort_flag) {
     // Give copies and MMAs that are still in flight time to land before shared memory and TMEM go away.
     const unsigned long long t0 = global_ns();
     while (global_ns() - t0 < 200000ull) {
     }
-    __syncthreads();
   }
+  // A CTA of a pair must not leave while its peer can still touch its shared memory or barriers.
+  if (kCtas == 2) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (kCtas == 2) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
+
+__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmParams p) { gemm_body<1>(p); }
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p) { gemm_body<2>(p); }
 
 // ---------------------------------------------------------------------------------------------
 // Host side
@@ -550,7 +697,7 @@ int encode_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols)
   return FP8GMM_OK;
 }
 
-uint32_t make_idesc(int a_format, int b_format) {
+uint32_t make_idesc(int a_format, int b_format, int ctas) {
   // tcgen05 instruction descriptor, kind::f8f6f4: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format
   // (0 = e4m3, 1 = e5m2), bits 15/16 = 0 (both operands K-major), [17,23) N >> 3, [24,29) M >> 4.
   uint32_t d = 0;
@@ -558,18 +705,42 @@ uint32_t make_idesc(int a_format, int b_format) {
   d |= static_cast<uint32_t>(a_format) << 7;
   d |= static_cast<uint32_t>(b_format) << 10;
   d |= static_cast<uint32_t>(kBlockN >> 3) << 17;
-  d |= static_cast<uint32_t>(kBlockM >> 4) << 24;
+  d |= static_cast<uint32_t>((kBlockM * ctas) >> 4) << 24;  // a CTA pair issues M = 256
   return d;
 }
 
-int launch(const GemmParams& p, cudaStream_t s) {
+// Profiling buffer installed with fp8gmm_set_gemm_profile_buffer (process-wide, NULL = off).
+long long* g_profile = nullptr;
+size_t g_profile_bytes = 0;
+
+int prefetch_distance() {
+  const char* e = getenv("FP8GMM_GEMM_PREFETCH");
+  return e ? atoi(e) : 0;
+}
+
+int launch(GemmParams& p, int ctas, cudaStream_t s) {
   // The attribute is per device and the call is idempotent and cheap, so it is simply repeated.
-  FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-  const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-  grouped_gemm_kernel<<<grid, kThreads, kSmemBytes, s>>>(p);
+  const int workers = sm_count() / ctas;
+  const int grid = ctas * (p.total_tiles < workers ? p.total_tiles : workers);
+  p.prefetch_kb = prefetch_distance();
+  p.profile = (g_profile != nullptr && g_profile_bytes >= static_cast<size_t>(grid) * 8 * sizeof(long long)) ? g_profile : nullptr;
+  if (ctas == 2) {
+    FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
+    grouped_gemm_pair_kernel<<<grid, kThreads, Cfg<2>::kSmemBytes, s>>>(p);
+  } else {
+    FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::kSmemBytes));
+    grouped_gemm_kernel<<<grid, kThreads, Cfg<1>::kSmemBytes, s>>>(p);
+  }
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;
+}
+
+// 0 = choose automatically, 1 / 2 = force single-CTA / paired tiles (FP8GMM_GEMM_CTAS, for experiments).
+int forced_ctas() {
+  const char* e = getenv("FP8GMM_GEMM_CTAS");
+  if (e == nullptr) return 0;
+  return e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0;
 }
 
 bool fmt_ok(int f) { return f == FP8GMM_E4M3 || f == FP8GMM_E5M2; }
@@ -600,14 +771,25 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   const int tile_n = a->activation == FP8GMM_ACT_SWIGLU ? kBlockN / 2 : kBlockN;
   const int64_t n_cols = a->activation == FP8GMM_ACT_SWIGLU ? a->n / 2 : a->n;
   const int64_t tiles_n = (n_cols + tile_n - 1) / tile_n;
+  // Paired 256-row tiles halve the operand traffic per SM; they pay off unless many groups are so small that
+  // rounding their rows up to 256 wastes much more than rounding up to 128.
+  int64_t pad128 = 0, pad256 = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t m = a->m_sizes[g];
+    FP8GMM_CHECK_ARG(m >= 0, "grouped_gemm: m_sizes[%d] is negative", g);
+    pad128 += (m + 127) / 128 * 128;
+    pad256 += (m + 255) / 256 * 256;
+  }
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = (pad256 * 10 <= pad128 * 11) ? 2 : 1;
+  const int tile_m = kBlockM * ctas;
   int64_t rows = 0, tiles = 0;
   p.tile_start[0] = 0;
   p.row_start[0] = 0;
   for (int g = 0; g < a->num_groups; ++g) {
     const int64_t m = a->m_sizes[g];
-    FP8GMM_CHECK_ARG(m >= 0, "grouped_gemm: m_sizes[%d] is negative", g);
     rows += m;
-    tiles += ((m + kBlockM - 1) / kBlockM) * tiles_n;
+    tiles += ((m + tile_m - 1) / tile_m) * tiles_n;
     FP8GMM_CHECK_ARG(rows <= INT32_MAX - 1024 && tiles <= INT32_MAX / 2, "grouped_gemm: problem too large");
     p.row_start[g + 1] = static_cast<int>(rows);
     p.tile_start[g + 1] = static_cast<int>(tiles);
@@ -645,8 +827,14 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.k = static_cast<int>(a->k);
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = static_cast<int>(tiles);
-  p.idesc = make_idesc(a->a_format, a->b_format);
-  return launch(p, static_cast<cudaStream_t>(stream));
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  return launch(p, ctas, static_cast<cudaStream_t>(stream));
+}
+
+int fp8gmm_set_gemm_profile_buffer(void* device_buffer, size_t bytes) {
+  fp8gmm::g_profile = static_cast<long long*>(device_buffer);
+  fp8gmm::g_profile_bytes = device_buffer ? bytes : 0;
+  return FP8GMM_OK;
 }
 
 size_t fp8gmm_wgrad_workspace_bytes(int num_groups) {
@@ -673,7 +861,9 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  const int64_t tiles_m = (a->n + kBlockM - 1) / kBlockM;
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
+  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
   const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
   FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad: problem too large");
   std::vector<CUtensorMap> maps(static_cast<size_t>(a->num_groups) * 2);
@@ -717,8 +907,8 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
   p.k = 0;
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
-  p.idesc = make_idesc(a->a_format, a->b_format);
-  return launch(p, s);
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  return launch(p, ctas, s);
 }
 
 }  // extern "C"

@@ -231,6 +231,18 @@ typedef struct {
 } fp8gmm_wgrad_args;
 
 size_t fp8gmm_wgrad_workspace_bytes(int num_groups);
+
+/*
+ * Profiling aid with no counterpart in the reference: while a device buffer of at least
+ * 8 * sizeof(int64) * (number of CTAs launched, at most 148) bytes is installed, every grouped-GEMM CTA
+ * writes its stall counters in SM clock cycles to buffer[cta*8 + i]:
+ *   0 producer waiting for a free shared-memory stage      1 MMA warp waiting for operands to land
+ *   2 MMA warp waiting for a free TMEM accumulator         3 MMA warp total
+ *   4 epilogue waiting for an accumulator                  5 epilogue busy (TMEM read, math, stores)
+ *   6 MMA warp inside the MMA / commit instructions        7 MMA warp total in nanoseconds (slot 3 / slot 7 = SM GHz)
+ * NULL removes it.  Process-wide; meant for one launch at a time under a benchmark, not for production.
+ */
+int fp8gmm_set_gemm_profile_buffer(void* device_buffer, size_t bytes);
 int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
