@@ -3,6 +3,7 @@
     python bench_kernels.py gemm  [--groups G --rows R --n N --k K --act none|gelu|swiglu --a-format e4m3|e5m2]
     python bench_kernels.py wgrad [--groups G --rows R --n N --k K]
     python bench_kernels.py step-gemms            # the six GEMMs of the Mixtral-shaped step, one by one
+    python bench_kernels.py scaled-mm [--groups G --rows R --n N --k K]   # library baseline: torch._scaled_mm per group
     python bench_kernels.py pad   [--groups G --max-rows M --cols K --mode cast|amax+cast|transpose|quantize]
                                                   # default = the pad-fusion microbenchmark: 256 groups, rows ~ U[0,4096],
                                                   # K = 7168, bf16 ~ N(0,3) with 0.1 % outliers x100
@@ -138,6 +139,31 @@ def wgrad_case(backend, dev, sizes, n, k, iters, warmup, label):
             "tflops": tf, "clocks": LAST_CLOCKS, "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
 
 
+def scaled_mm_case(dev, sizes, n, k, iters, warmup, label):
+    """Library comparison (not product code): the per-group cuBLASLt FP8 loop, torch._scaled_mm per group,
+    which is what the reference's Transformer-Engine path amounts to on this GPU (reference
+    fp8_gmm/backend.py:84-96)."""
+    G, m = len(sizes), sum(sizes)
+    a = rand_fp8((m, k), E4, dev, 1)
+    b = rand_fp8((G, n, k), E4, dev, 2)
+    one = torch.ones((), device=dev)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    offs = [0]
+    for s_ in sizes:
+        offs.append(offs[-1] + s_)
+
+    def fn():
+        for g in range(G):
+            torch._scaled_mm(a[offs[g]:offs[g + 1]], b[g].t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16,
+                             out=c[offs[g]:offs[g + 1]])
+
+    ms = time_ms(fn, iters, warmup)
+    _, bf16, src = peaks()
+    tf = 2.0 * m * n * k / ms / 1e9
+    return {"kernel": "torch._scaled_mm per group (cuBLASLt, library baseline)", "case": label, "groups": G, "rows": m,
+            "n": n, "k": k, "ms": ms, "tflops": tf, "clocks": LAST_CLOCKS, "frac_of_2x_bf16_" + src: tf / (2 * bf16)}
+
+
 def pad_case(backend, dev, args):
     g = torch.Generator().manual_seed(0)
     rows = torch.randint(0, args.max_rows + 1, (args.groups,), generator=g).tolist()
@@ -184,7 +210,7 @@ def pad_case(backend, dev, args):
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "wgrad", "step-gemms", "pad"])
+    p.add_argument("what", choices=["gemm", "wgrad", "step-gemms", "pad", "scaled-mm"])
     p.add_argument("--groups", type=int, default=None)
     p.add_argument("--rows", type=int, default=32768)
     p.add_argument("--n", type=int, default=4096)
@@ -205,6 +231,9 @@ def main():
         sizes = even_sizes(args.groups or 8, args.rows)
         print(json.dumps(gemm_case(backend, dev, sizes, args.n, args.k, args.act, E4 if args.a_format == "e4m3" else E5,
                                    args.iters, args.warmup, "custom")))
+    elif args.what == "scaled-mm":
+        sizes = even_sizes(args.groups or 8, args.rows)
+        print(json.dumps(scaled_mm_case(dev, sizes, args.n, args.k, args.iters, args.warmup, "custom")))
     elif args.what == "wgrad":
         sizes = even_sizes(args.groups or 8, args.rows)
         print(json.dumps(wgrad_case(backend, dev, sizes, args.n, args.k, args.iters, args.warmup, "custom")))
