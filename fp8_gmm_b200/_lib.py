@@ -76,6 +76,7 @@ SYMBOLS = {
     "fp8gmm_grouped_gemm": (ctypes.c_int, [ctypes.POINTER(GemmArgs), c_vp]),
     "fp8gmm_wgrad_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int]),
     "fp8gmm_grouped_wgrad": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
+    "fp8gmm_grouped_wgrad_static": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_set_gemm_profile_buffer": (ctypes.c_int, [c_vp, ctypes.c_size_t]),
     "fp8gmm_delayed_scaling_update": (
         ctypes.c_int,

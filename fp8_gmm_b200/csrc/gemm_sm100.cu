@@ -912,3 +912,124 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Weight gradient without a caller-provided workspace
+// ---------------------------------------------------------------------------------------------
+// fp8gmm_grouped_wgrad needs device scratch for its per-group TMA descriptors and takes it from the
+// caller.  Some callers have no device memory to give and cannot get any: a training framework that has
+// already claimed the whole GPU for its own memory pool (a fresh cudaMalloc then fails, or stalls, because
+// cudaMalloc and cudaFree synchronise the device), or a host runtime whose plug-in contract forbids device
+// allocation once it is running.  For them the same kernel is offered with its scratch in a fixed array
+// that is part of the library image: every GPU that loads the library holds these
+// kStaticWgradMaxGroups * 2 * 128 bytes = 32 KiB until the process exits.
+//
+// What a caller has to know:
+//   * at most kStaticWgradMaxGroups (128) groups per call; more is rejected with FP8GMM_UNSUPPORTED;
+//   * the call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine;
+//   * the first call on each device looks up the array's device address (the name of a __device__ array is
+//     only a host-side handle, not an address a kernel can use) with that device current; make that first
+//     call before starting any stream capture;
+//   * all calls on a device share the one array and each call overwrites all of the part it uses, so
+//     nothing from an earlier call is ever read; but two calls whose work overlaps on the GPU (different
+//     streams, no ordering between them) race on it.  Issue them on one stream or order them yourself.
+constexpr int kStaticWgradMaxGroups = 128;
+static __device__ __align__(256) unsigned char g_static_wgrad_maps[kStaticWgradMaxGroups * 2 * sizeof(CUtensorMap)];
+
+namespace fp8gmm {
+namespace {
+CUtensorMap* g_static_wgrad_addr[64] = {nullptr};
+std::mutex g_static_wgrad_mutex;
+
+// Device address of g_static_wgrad_maps on the current device, resolved once per device.
+int static_wgrad_scratch(CUtensorMap** out) {
+  int dev = 0;
+  FP8GMM_CHECK_CUDA(cudaGetDevice(&dev));
+  FP8GMM_CHECK_ARG(dev >= 0 && dev < 64, "grouped_wgrad_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_wgrad_mutex);
+  if (g_static_wgrad_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    FP8GMM_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_static_wgrad_maps));
+    g_static_wgrad_addr[dev] = static_cast<CUtensorMap*>(ptr);
+  }
+  *out = g_static_wgrad_addr[dev];
+  return FP8GMM_OK;
+}
+}  // namespace
+}  // namespace fp8gmm
+
+extern "C" int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* a, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(a != nullptr, "grouped_wgrad_static: NULL arguments");
+  if (a->num_groups > kStaticWgradMaxGroups) {
+    set_error("grouped_wgrad_static: %d groups exceed the %d this allocation-free entry point supports; "
+              "use fp8gmm_grouped_wgrad with a workspace", a->num_groups, kStaticWgradMaxGroups);
+    return FP8GMM_UNSUPPORTED;
+  }
+  FP8GMM_CHECK_ARG(a->num_groups >= 0, "grouped_wgrad_static: negative num_groups");
+  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_wgrad_static: bad fp8 format");
+  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
+                   "grouped_wgrad_static: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n,
+                   (long long)a->k);
+  if (a->num_groups == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "grouped_wgrad_static: NULL pointer");
+  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_wgrad_static: NULL scale_inv pointer");
+  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
+                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0,
+                   "grouped_wgrad_static: operand pointers must be 16-byte aligned");
+  CUtensorMap* scratch = nullptr;
+  int rc = static_wgrad_scratch(&scratch);
+  if (rc != FP8GMM_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
+  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
+  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
+  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad_static: problem too large");
+  CUtensorMap maps[kStaticWgradMaxGroups * 2];  // host staging on the stack: no heap, no device allocation
+  memset(maps, 0, sizeof(CUtensorMap) * 2 * static_cast<size_t>(a->num_groups));
+  p.tile_start[0] = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
+    const int64_t len = o1 - o0;
+    FP8GMM_CHECK_ARG(len >= 0 && len % 16 == 0 && o1 <= INT32_MAX - 1024,
+                     "grouped_wgrad_static: group %d contraction length %lld must be a non-negative multiple of 16", g,
+                     (long long)len);
+    p.row_start[g] = static_cast<int>(o0);
+    p.row_start[g + 1] = static_cast<int>(o1);
+    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
+    if (len > 0) {
+      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "grouped_wgrad_static: NULL operand pointer");
+      rc = encode_map(&maps[2 * g], static_cast<const char*>(a->a_t) + o0 * a->n, static_cast<uint64_t>(a->n),
+                      static_cast<uint64_t>(len));
+      if (rc != FP8GMM_OK) return rc;
+      rc = encode_map(&maps[2 * g + 1], static_cast<const char*>(a->b_t) + o0 * a->k, static_cast<uint64_t>(a->k),
+                      static_cast<uint64_t>(len));
+      if (rc != FP8GMM_OK) return rc;
+    }
+  }
+  // Overwrites every descriptor slot this launch reads (empty groups get zeroed slots that are never used).
+  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(scratch, maps, sizeof(CUtensorMap) * 2 * static_cast<size_t>(a->num_groups),
+                                    cudaMemcpyHostToDevice, s));
+  p.maps = scratch;
+  p.c = static_cast<uint16_t*>(a->c);
+  p.sa = a->a_scale_inv;
+  p.sb = a->b_scale_inv;
+  p.sa_stride = a->a_scale_inv_stride;
+  p.sb_stride = a->b_scale_inv_stride;
+  p.ldc = a->k;
+  p.status = device_status_word();
+  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_wgrad_static: cannot resolve the device status word");
+  p.mode = kModeWgrad;
+  p.activation = FP8GMM_ACT_NONE;
+  p.num_groups = a->num_groups;
+  p.n = static_cast<int>(a->k);
+  p.m_fixed = static_cast<int>(a->n);
+  p.k = 0;
+  p.tiles_n = static_cast<int>(tiles_n);
+  p.total_tiles = p.tile_start[a->num_groups];
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  return launch(p, ctas, s);
+}

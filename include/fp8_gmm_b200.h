@@ -233,6 +233,23 @@ typedef struct {
 size_t fp8gmm_wgrad_workspace_bytes(int num_groups);
 
 /*
+ * fp8gmm_grouped_wgrad for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Same arguments and results as fp8gmm_grouped_wgrad, except that `workspace` and
+ * `workspace_bytes` are ignored: the per-group TMA descriptors go into a fixed 32 KiB array inside the
+ * library image (held by every GPU that loads the library, until the process exits) instead of into
+ * caller memory.  It is meant for hosts that own all device memory themselves -- a framework whose pool
+ * has already reserved the GPU, so a fresh cudaMalloc would fail or stall the device, or a runtime that
+ * forbids plug-ins to allocate after start-up.  Limits and rules:
+ *   - at most 128 groups per call; more returns FP8GMM_UNSUPPORTED with a message;
+ *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - the first call on each device resolves the array's device address (with that device current): make
+ *     that first call before any stream capture begins;
+ *   - all calls on one device share the array; each call rewrites every slot it reads, but calls whose GPU
+ *     work may overlap (different streams without ordering) race on it -- keep them on one stream.
+ */
+int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* args, void* stream);
+
+/*
  * Profiling aid with no counterpart in the reference: while a device buffer of at least
  * 8 * sizeof(int64) * (number of CTAs launched, at most 148) bytes is installed, every grouped-GEMM CTA
  * writes its stall counters in SM clock cycles to buffer[cta*8 + i]:
