@@ -307,7 +307,7 @@ def main():
         else:
             from fp8_gmm_b200 import ep_bench
 
-            reference_arm(args, ep_bench.WORKLOAD_NAME, ep_bench.H, ep_bench.F, ep_bench.ROWS_PER_EXPERT)
+            reference_arm(args, ep_bench.WORKLOAD_NAME, ep_bench.H, ep_bench.F, ep_bench.ROWS_PER_EXPERT * 8)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: fp8_gmm_b200 has no CPU path (use --impl reference for the CPU baseline)")

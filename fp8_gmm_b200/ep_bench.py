@@ -1,0 +1,170 @@
+"""Expert-parallel leg of bench.py: one rank per GPU, NCCL all-to-all dispatch / combine around GroupedMlp.
+
+Workload (synthetic, seeded; BASELINE config 4): 128 experts split evenly over the ranks, hidden 4096, ffn 1536,
+SwiGLU, 32768 tokens per GPU routed top-8 (softmax over N(0,1) logits, 8 distinct experts per token) = 262144
+routed rows per GPU, delayed scaling with an amax history of 16.  Weak scaling: the per-GPU work is fixed.
+"""
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+E, H, F, TOKENS_PER_GPU, TOPK = 128, 4096, 1536, 32768, 8
+ROWS_PER_EXPERT = TOKENS_PER_GPU * TOPK // E  # per source rank; used to size the CPU baseline sample
+WORKLOAD_NAME = ("expert-parallel GroupedMLP (E=128 split over the ranks, hidden 4096, ffn 1536, SwiGLU, "
+                 "32768 tokens/GPU top-8, all-to-all dispatch/combine)")
+
+
+def routed_sizes(seed):
+    g = torch.Generator().manual_seed(seed)
+    probs = torch.softmax(torch.randn(TOKENS_PER_GPU, E, generator=g), dim=-1)
+    picks = torch.multinomial(probs, TOPK, replacement=False, generator=g)
+    return torch.bincount(picks.reshape(-1), minlength=E)
+
+
+def _timed(fn, steps, world):
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    secs = torch.tensor([start.elapsed_time(end) / 1e3], device="cuda")
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(secs, op=dist.ReduceOp.MAX)
+    return float(secs)
+
+
+def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
+    import fp8_gmm_b200 as fg
+    from fp8_gmm_b200 import backend, ep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    sizes = routed_sizes(1000 + rank)
+    rows = int(sizes.sum())
+    g = torch.Generator().manual_seed(2000 + rank)
+    x_host = torch.randn(rows, H, generator=g).to(torch.bfloat16).pin_memory()
+    dy_host = torch.randn(rows, H, generator=g).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
+    gi_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
+    torch.manual_seed(3000 + rank)
+    model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu")
+    with torch.no_grad():
+        model.mlp.fc1_weight.normal_(0.0, 0.02)
+        model.mlp.fc2_weight.normal_(0.0, 0.02)
+    x_dev = x_host.to(dev).requires_grad_(True)
+    dy_dev = dy_host.to(dev)
+    recipe = fg.DelayedScaling(amax_history_len=16)
+
+    def step():
+        model.mlp.fc1_weight.grad = None
+        model.mlp.fc2_weight.grad = None
+        x_dev.grad = None
+        with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+            out = model(x_dev, sizes)
+        out.backward(dy_dev)
+        return out
+
+    def step_e2e():
+        x_dev.data.copy_(x_host, non_blocking=True)
+        dy_dev.copy_(dy_host, non_blocking=True)
+        out = step()
+        out_host.copy_(out.detach(), non_blocking=True)
+        gi_host.copy_(x_dev.grad, non_blocking=True)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    backend.device_status()
+
+    timings = []
+    backend.set_gemm_timings(timings)
+    launches0 = backend.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        secs = _timed(step, args.steps, world)
+    launches = backend.launch_count() - launches0
+    backend.set_gemm_timings(None)
+    gemm_ms = sum(s.elapsed_time(e) for s, e, _ in timings)
+    gemm_flops_local = sum(f for _, _, f in timings)
+
+    for _ in range(2):
+        step_e2e()
+    secs_e2e = _timed(step_e2e, args.steps, world)
+
+    # the same local problem without the exchange (what this rank's experts compute), for the EP efficiency figure
+    local_secs = None
+    if world > 1:
+        plan = ep.make_plan(sizes, dev)
+        local_rows = int(plan.local_group_sizes.sum())
+        lx = torch.randn(local_rows, H, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+        ldy = torch.randn(local_rows, H, device=dev, dtype=torch.bfloat16)
+
+        def local_step():
+            model.mlp.fc1_weight.grad = None
+            model.mlp.fc2_weight.grad = None
+            lx.grad = None
+            with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+                o = model.mlp(lx, plan.local_group_sizes)
+            o.backward(ldy)
+
+        for _ in range(3):
+            local_step()
+        local_secs = _timed(local_step, args.steps, world)
+    backend.device_status()
+
+    total_rows = torch.tensor([float(rows)], device=dev)
+    if world > 1:
+        dist.all_reduce(total_rows)
+    flops = 18.0 * float(total_rows) * H * F  # every routed row is processed exactly once, on the rank owning its expert
+    if rank == 0:
+        peak_fp8 = 2.0 * peaks["bf16_sustained"]
+        value = flops * args.steps / secs / 1e12
+        achieved = gemm_flops_local / (gemm_ms / 1e3) / 1e12
+        line = {
+            "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8 (e4m3 fwd / e5m2 grad, fp32 accumulate in TMEM, bf16 out)", "data": "synthetic",
+            "config": {"workload": WORKLOAD_NAME, "parallelism": f"ep{world}", "experts_per_gpu": E // world,
+                       "routed_rows_per_gpu": TOKENS_PER_GPU * TOPK,
+                       "l2": "operands (2.1 GB of activations per GPU per exchange, 0.2-2.4 GB of weights) exceed the 126 MB L2",
+                       "recipe": "delayed scaling, amax history 16"},
+            "tokens_per_s": TOKENS_PER_GPU * world * args.steps / secs,
+            "tokens_per_s_per_gpu": TOKENS_PER_GPU * args.steps / secs,
+            "frac_of_nominal_fp8_peak": value / (4500.0 * world),
+            "clocks": clocks.summary(),
+            "e2e": {"value": flops * args.steps / secs_e2e / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (x_host.numel() + dy_host.numel()) * 2 * world,
+                    "d2h_bytes_per_step": (out_host.numel() + gi_host.numel()) * 2 * world,
+                    "ms_per_step": secs_e2e / args.steps * 1e3},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": "grouped_gemm kernels on rank 0 (tcgen05, 6 launches per step)", "bound": "tensor",
+                         "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s", "frac": achieved / peak_fp8,
+                         "peak_source": f"2 x {peaks['source']} dense bf16 sustained ({peaks['bf16_sustained']} TFLOP/s)",
+                         "frac_of_nominal_4500": achieved / 4500.0, "launches_timed": len(timings),
+                         "mean_launch_ms": gemm_ms / max(len(timings), 1),
+                         "flops_per_launch": gemm_flops_local / max(len(timings), 1),
+                         "gemm_share_of_step": (gemm_ms / 1e3) / secs, "traffic": None},
+        }
+        if local_secs is not None:
+            line["ep"] = {"local_ms_per_step_without_exchange": local_secs / args.steps * 1e3,
+                          "efficiency_vs_local": local_secs / secs}
+        if world == 1 and not args.no_cpu_baseline:
+            cstep, cflops, desc = cpu_sample_step(H, F, ROWS_PER_EXPERT * 8)
+            ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)
+            line["cpu_baseline"] = {"value": ctf, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
