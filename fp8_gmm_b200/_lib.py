@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfp8gmm_b200.so")
+# FP8GMM_LIBRARY selects another build of the same library (e.g. one compiled with experimental tile sizes)
+LIB_PATH = os.environ.get("FP8GMM_LIBRARY") or os.path.join(_HERE, "libfp8gmm_b200.so")
 
 c_i64 = ctypes.c_int64
 c_vp = ctypes.c_void_p

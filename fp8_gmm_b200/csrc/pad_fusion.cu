@@ -16,8 +16,13 @@
 // the row-wise reads are bank-conflict free) and the CTA then writes 128 contiguous bytes per column
 // (8 lanes x 16 bytes), i.e. full 128-byte lines whenever padded_rows is a multiple of 16.  Ragged
 // shapes (cols % 8, unaligned bases, padded_rows % 16) take predicated scalar accesses in the same
-// kernel; there is no second "unaligned" launch.  The tensor table travels in the parameter block
+// kernel; there is no second "unaligned" launch.  The kernel is latency bound unless enough loads are in
+// flight (ncu: long-scoreboard was the top stall at 51 % of DRAM peak when the compiler interleaved loads and
+// use), so all 16 row loads of a thread are issued before the first use.  (A variant that staged input tiles
+// with cp.async.bulk row copies was measured slower -- 128 small bulk copies per tile cost more than they hide
+// -- and taller tiles, 256 or 512 rows, were slower too.)  The tensor table travels in the parameter block
 // (no cap on the number of tensors per call: the host splits long lists into launches of kMaxTensors).
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
@@ -25,8 +30,13 @@
 namespace fp8gmm {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kTileRows = 128;
+#ifndef FP8GMM_PAD_WARPS
+#define FP8GMM_PAD_WARPS 8
+#endif
+constexpr int kWarps = FP8GMM_PAD_WARPS;  // each warp owns 16 rows of the tile
+constexpr int kThreads = 32 * kWarps;
+constexpr int kTileRows = 16 * kWarps;
+constexpr int kChunks = kTileRows / 16;   // 16-byte row chunks per transposed column
 constexpr int kTileCols = 256;
 constexpr int kMaxTensors = 256;
 
@@ -63,9 +73,9 @@ __device__ __forceinline__ float dgelu_tanh(float x) {
 __device__ __forceinline__ uint32_t put_byte(uint32_t word, uint32_t b, int pos) { return word | (b << (8 * pos)); }
 
 template <int kMode, int kFormat>
-__global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_constant__ PadArgs args) {
+__global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspose) ? 3 : 1) multi_pad_kernel(const __grid_constant__ PadArgs args) {
   constexpr int kHalves = (kMode == kDswiglu) ? 2 : 1;
-  __shared__ __align__(16) uint8_t smem_t[kTileCols * kTileRows];  // [col][128 bytes of rows], swizzled
+  extern __shared__ __align__(16) uint8_t smem_t[];  // [col][kTileRows bytes of rows], 16-byte chunks XOR-swizzled
   __shared__ float staging[kThreads / 32];
 
   const int tile = blockIdx.x;
@@ -95,6 +105,13 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
   // ---- phase 1: load, convert, row-major store, pack the transposed bytes in registers --------
   if (kMode == kTranspose) {
     const uint8_t* in = static_cast<const uint8_t*>(d.in);
+    // all 16 row loads are issued before the first use, so 16 x 8 bytes per thread are in flight
+    uint2 pre[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      pre[i] = make_uint2(0, 0);
+      if (fast_io && row0 + i < rows && col0 < cols) pre[i] = ld_stream8(in + (int64_t)(row0 + i) * ld_in + col0);
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int row = row0 + i;
@@ -102,9 +119,8 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
       if (row < rows && col0 < cols) {
         const uint8_t* p = in + (int64_t)row * ld_in + col0;
         if (fast_io) {
-          const uint2 v = ld_stream8(p);
-          lo = v.x;
-          hi = v.y;
+          lo = pre[i].x;
+          hi = pre[i].y;
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -123,6 +139,13 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
   } else {
     const uint16_t* in = static_cast<const uint16_t*>(d.in);
     const uint16_t* in2 = static_cast<const uint16_t*>(d.in2);
+    // all 16 row loads of `in` are issued before the first use: 256 bytes per thread in flight
+    uint4 pre[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      pre[i] = make_uint4(0, 0, 0, 0);
+      if (fast_io && row0 + i < rows && col0 < cols) pre[i] = ld_stream16(in + (int64_t)(row0 + i) * ld_in + col0);
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int row = row0 + i;
@@ -132,7 +155,7 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
       const bool live = row < rows && col0 < cols;
       if (live) {
         if (fast_io) {
-          const uint4 v = ld_stream16(in + (int64_t)row * ld_in + col0);
+          const uint4 v = pre[i];
           const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) x[2 * j] = bf16_lo(w[j]), x[2 * j + 1] = bf16_hi(w[j]);
@@ -219,7 +242,7 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
           const int idx = it * kThreads + tid;
-          const int c = idx >> 3, chunk = idx & 7;
+          const int c = idx / kChunks, chunk = idx % kChunks;
           const int col = tile_col + c, row = tile_row + chunk * 16;
           if (col < cols && row < padded_rows) {
             const uint4 v = *reinterpret_cast<const uint4*>(smem_t + c * kTileRows + ((chunk ^ ((c >> 3) & 7)) << 4));
@@ -228,7 +251,7 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
         }
       } else {
         for (int idx = tid; idx < kTileCols * kTileRows; idx += kThreads) {
-          const int c = idx >> 7, r = idx & 127;
+          const int c = idx / kTileRows, r = idx % kTileRows;
           const int col = tile_col + c, row = tile_row + r;
           if (col < cols && row < padded_rows)
             out_t[(int64_t)col * padded_rows + row] =
@@ -254,76 +277,86 @@ __global__ void __launch_bounds__(kThreads) multi_pad_kernel(const __grid_consta
 template <int kMode>
 int launch_mode(const PadArgs& args, int out_format, cudaStream_t s) {
   const int grid = args.tile_start[args.num];
-  if (kMode == kTranspose || out_format == FP8GMM_E4M3)
-    multi_pad_kernel<kMode, FP8GMM_E4M3><<<grid, kThreads, 0, s>>>(args);
-  else
-    multi_pad_kernel<kMode, FP8GMM_E5M2><<<grid, kThreads, 0, s>>>(args);
+  constexpr int kSmem = kTileCols * kTileRows;
+  if (kMode == kTranspose || out_format == FP8GMM_E4M3) {
+    if (kSmem > 48 * 1024)
+      FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(multi_pad_kernel<kMode, FP8GMM_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    multi_pad_kernel<kMode, FP8GMM_E4M3><<<grid, kThreads, kSmem, s>>>(args);
+  } else {
+    if (kSmem > 48 * 1024)
+      FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(multi_pad_kernel<kMode, FP8GMM_E5M2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    multi_pad_kernel<kMode, FP8GMM_E5M2><<<grid, kThreads, kSmem, s>>>(args);
+  }
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;
+}
+
+int flush(PadArgs& args, int mode, int out_format, cudaStream_t s) {
+  if (args.num == 0) return FP8GMM_OK;
+  int rc = FP8GMM_OK;
+  switch (mode) {
+    case kCast: rc = launch_mode<kCast>(args, out_format, s); break;
+    case kDgelu: rc = launch_mode<kDgelu>(args, out_format, s); break;
+    case kDswiglu: rc = launch_mode<kDswiglu>(args, out_format, s); break;
+    default: rc = launch_mode<kTranspose>(args, out_format, s); break;
+  }
+  args.num = 0;
+  args.tile_start[0] = 0;
+  return rc;
 }
 
 int run(const fp8gmm_tensor_desc* descs, int count, int mode, int out_format, void* stream, const char* name) {
   FP8GMM_CHECK_ARG(count >= 0 && (count == 0 || descs != nullptr), "%s: bad descriptor list", name);
   FP8GMM_CHECK_ARG(out_format == FP8GMM_E4M3 || out_format == FP8GMM_E5M2, "%s: bad fp8 format %d", name, out_format);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  PadArgs args;
+  // The tensor table is launched whenever the parameter block is full and once at the end.
+  PadArgs direct;
+  direct.num = 0;
+  direct.tile_start[0] = 0;
   const int in_elem = mode == kTranspose ? 1 : 2;
-  int i = 0;
-  while (i < count) {
-    args.num = 0;
-    args.tile_start[0] = 0;
-    for (; i < count && args.num < kMaxTensors; ++i) {
-      const fp8gmm_tensor_desc& t = descs[i];
-      FP8GMM_CHECK_ARG(t.rows >= 0 && t.cols >= 0, "%s: tensor %d has a negative size", name, i);
-      FP8GMM_CHECK_ARG(t.rows <= INT32_MAX - 256 && t.cols <= INT32_MAX / 2 - 256, "%s: tensor %d is too large", name, i);
-      const int64_t cover_rows = t.out_t ? t.padded_rows : t.rows;
-      FP8GMM_CHECK_ARG(!t.out_t || (t.padded_rows >= t.rows && t.padded_rows <= INT32_MAX - 256),
-                       "%s: tensor %d: padded_rows %lld < rows %lld", name, i, (long long)t.padded_rows,
-                       (long long)t.rows);
-      if (cover_rows == 0 || t.cols == 0) continue;
-      FP8GMM_CHECK_ARG(t.in != nullptr || t.rows == 0, "%s: tensor %d has a NULL input", name, i);
-      FP8GMM_CHECK_ARG(mode == kCast || mode == kTranspose || t.in2 != nullptr || t.rows == 0,
-                       "%s: tensor %d has a NULL second input", name, i);
-      FP8GMM_CHECK_ARG(mode != kTranspose || t.out_t != nullptr, "%s: tensor %d has a NULL transposed output", name, i);
-      const int64_t tiles_m = (cover_rows + kTileRows - 1) / kTileRows;
-      const int64_t tiles_n = (t.cols + kTileCols - 1) / kTileCols;
-      const int64_t tiles = tiles_m * tiles_n;
-      FP8GMM_CHECK_ARG(tiles <= INT32_MAX / 2, "%s: tensor %d is too large", name, i);
-      if (tiles + args.tile_start[args.num] > INT32_MAX) break;
-      PadDesc& p = args.d[args.num];
-      p.in = t.in;
-      p.in2 = t.in2;
-      p.out = mode == kTranspose ? nullptr : static_cast<uint8_t*>(t.out);
-      p.out_t = static_cast<uint8_t*>(t.out_t);
-      p.scale = t.scale;
-      p.amax = t.amax;
-      p.rows = static_cast<int>(t.rows);
-      p.cols = static_cast<int>(t.cols);
-      p.padded_rows = static_cast<int>(cover_rows);
-      p.tiles_n = static_cast<int>(tiles_n);
-      const uintptr_t in_bits = reinterpret_cast<uintptr_t>(t.in) | reinterpret_cast<uintptr_t>(t.in2);
-      const int in_align = in_elem == 2 ? 16 : 8;
-      p.fast_io = (t.cols % 8 == 0) && (in_bits % in_align == 0) && (reinterpret_cast<uintptr_t>(t.out) % 8 == 0);
-      p.fast_t = (cover_rows % 16 == 0) && (reinterpret_cast<uintptr_t>(t.out_t) % 16 == 0);
-      p.pad0 = p.pad1 = 0;
-      args.tile_start[args.num + 1] = args.tile_start[args.num] + static_cast<int>(tiles);
-      ++args.num;
+  for (int i = 0; i < count; ++i) {
+    const fp8gmm_tensor_desc& t = descs[i];
+    FP8GMM_CHECK_ARG(t.rows >= 0 && t.cols >= 0, "%s: tensor %d has a negative size", name, i);
+    FP8GMM_CHECK_ARG(t.rows <= INT32_MAX - 256 && t.cols <= INT32_MAX / 2 - 256, "%s: tensor %d is too large", name, i);
+    const int64_t cover_rows = t.out_t ? t.padded_rows : t.rows;
+    FP8GMM_CHECK_ARG(!t.out_t || (t.padded_rows >= t.rows && t.padded_rows <= INT32_MAX - 256),
+                     "%s: tensor %d: padded_rows %lld < rows %lld", name, i, (long long)t.padded_rows, (long long)t.rows);
+    if (cover_rows == 0 || t.cols == 0) continue;
+    FP8GMM_CHECK_ARG(t.in != nullptr || t.rows == 0, "%s: tensor %d has a NULL input", name, i);
+    FP8GMM_CHECK_ARG(mode == kCast || mode == kTranspose || t.in2 != nullptr || t.rows == 0,
+                     "%s: tensor %d has a NULL second input", name, i);
+    FP8GMM_CHECK_ARG(mode != kTranspose || t.out_t != nullptr, "%s: tensor %d has a NULL transposed output", name, i);
+    const int64_t tiles_m = (cover_rows + kTileRows - 1) / kTileRows;
+    const int64_t tiles_n = (t.cols + kTileCols - 1) / kTileCols;
+    const int64_t tiles = tiles_m * tiles_n;
+    FP8GMM_CHECK_ARG(tiles <= INT32_MAX / 2, "%s: tensor %d is too large", name, i);
+    PadDesc p;
+    p.in = t.in;
+    p.in2 = t.in2;
+    p.out = mode == kTranspose ? nullptr : static_cast<uint8_t*>(t.out);
+    p.out_t = static_cast<uint8_t*>(t.out_t);
+    p.scale = t.scale;
+    p.amax = t.amax;
+    p.rows = static_cast<int>(t.rows);
+    p.cols = static_cast<int>(t.cols);
+    p.padded_rows = static_cast<int>(cover_rows);
+    p.tiles_n = static_cast<int>(tiles_n);
+    const uintptr_t in_bits = reinterpret_cast<uintptr_t>(t.in) | reinterpret_cast<uintptr_t>(t.in2);
+    const int in_align = in_elem == 2 ? 16 : 8;
+    p.fast_io = (t.cols % 8 == 0) && (in_bits % in_align == 0) && (reinterpret_cast<uintptr_t>(t.out) % 8 == 0);
+    p.fast_t = (cover_rows % 16 == 0) && (reinterpret_cast<uintptr_t>(t.out_t) % 16 == 0);
+    p.pad0 = p.pad1 = 0;
+    PadArgs& dst = direct;
+    if (dst.num == kMaxTensors || tiles + dst.tile_start[dst.num] > INT32_MAX) {
+      const int rc = flush(dst, mode, out_format, s);
+      if (rc != FP8GMM_OK) return rc;
     }
-    if (args.num == 0) {
-      FP8GMM_CHECK_ARG(i >= count, "%s: tensor %d is too large for one launch", name, i);
-      continue;
-    }
-    int rc = FP8GMM_OK;
-    switch (mode) {
-      case kCast: rc = launch_mode<kCast>(args, out_format, s); break;
-      case kDgelu: rc = launch_mode<kDgelu>(args, out_format, s); break;
-      case kDswiglu: rc = launch_mode<kDswiglu>(args, out_format, s); break;
-      default: rc = launch_mode<kTranspose>(args, out_format, s); break;
-    }
-    if (rc != FP8GMM_OK) return rc;
+    dst.d[dst.num] = p;
+    dst.tile_start[dst.num + 1] = dst.tile_start[dst.num] + static_cast<int>(tiles);
+    ++dst.num;
   }
-  return FP8GMM_OK;
+  return flush(direct, mode, out_format, s);
 }
 
 }  // namespace
