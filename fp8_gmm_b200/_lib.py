@@ -47,6 +47,18 @@ class GemmArgs(ctypes.Structure):
         ("activation", ctypes.c_int), ("act_out", c_vp),
         ("act_scale", c_fp), ("act_scale_stride", c_i64),
         ("act_amax", c_fp), ("act_amax_stride", c_i64),
+        ("c_row_map", c_vp),
+    ]
+
+
+class BlockedCastArgs(ctypes.Structure):
+    _fields_ = [
+        ("in_", c_vp), ("out", c_vp),
+        ("src_start", ctypes.POINTER(c_i64)), ("dst_start", ctypes.POINTER(c_i64)),
+        ("rows", ctypes.POINTER(c_i64)), ("group", ctypes.POINTER(c_i64)),
+        ("num_blocks", c_i64), ("cols", c_i64),
+        ("scale", c_fp), ("scale_stride", c_i64), ("amax", c_fp), ("amax_stride", c_i64),
+        ("out_format", ctypes.c_int),
     ]
 
 
@@ -74,6 +86,7 @@ SYMBOLS = {
     "fp8gmm_multi_pad_cast_transpose_dswiglu": (ctypes.c_int, [ctypes.POINTER(TensorDesc), ctypes.c_int, ctypes.c_int, c_vp]),
     "fp8gmm_multi_scale_mul": (ctypes.c_int, [ctypes.POINTER(ScaleMulDesc), ctypes.c_int, c_vp]),
     "fp8gmm_grouped_pad_cast_transpose": (ctypes.c_int, [ctypes.POINTER(GroupedCastArgs), c_vp]),
+    "fp8gmm_blocked_cast": (ctypes.c_int, [ctypes.POINTER(BlockedCastArgs), c_vp]),
     "fp8gmm_grouped_gemm": (ctypes.c_int, [ctypes.POINTER(GemmArgs), c_vp]),
     "fp8gmm_wgrad_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int]),
     "fp8gmm_grouped_wgrad": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),

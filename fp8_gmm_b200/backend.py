@@ -14,7 +14,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import GemmArgs, GroupedCastArgs, ScaleMulDesc, TensorDesc, WgradArgs, check, lib
+from ._lib import BlockedCastArgs, GemmArgs, GroupedCastArgs, ScaleMulDesc, TensorDesc, WgradArgs, check, lib
 from .utils import FP8_FORMAT_CODE
 
 _FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
@@ -287,7 +287,42 @@ def grouped_cast_transpose(inp, row_offsets, out, out_t, t_offsets, scale, amax,
 # ------------------------------------------------------------------------------------------------
 # GEMMs (reference fp8_gmm/backend.py:25-97)
 # ------------------------------------------------------------------------------------------------
-def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax):
+class RowPermutation:
+    """Block permutation between an external row order and the expert-major order the grouped kernels use.
+
+    Block b is ``rows[b]`` consecutive rows that sit at external row ``src_start[b]`` and belong at expert-major
+    row ``dst_start[b]`` of group ``group[b]`` (host int64 sequences).  ``row_map`` is the same permutation per
+    row as a device int32 tensor: expert-major row r <-> external row row_map[r].  Used by expert parallelism,
+    where the all-to-all delivers rows source-major."""
+
+    def __init__(self, src_start, dst_start, rows, group, row_map):
+        self.num_blocks = len(rows)
+        self._keep = [_i64_array(v) for v in (src_start, dst_start, rows, group)]
+        self.src_start, self.dst_start, self.rows, self.group = [k[0] for k in self._keep]
+        self.row_map = row_map
+        assert row_map.dtype == torch.int32 and row_map.is_cuda and row_map.is_contiguous()
+
+
+def blocked_cast(inp, out, perm, scale, amax, num_groups):
+    """bf16 rows in external order -> fp8 rows in expert-major order (+ per-group amax); see fp8gmm_blocked_cast."""
+    _cuda_2d(inp, "inp", (torch.bfloat16,))
+    _cuda_2d(out, "out", _FP8)
+    _require(inp.shape == out.shape, "blocked_cast: shapes differ")
+    args = BlockedCastArgs()
+    args.in_, args.out = inp.data_ptr(), out.data_ptr()
+    args.src_start, args.dst_start, args.rows, args.group = perm.src_start, perm.dst_start, perm.rows, perm.group
+    args.num_blocks, args.cols = perm.num_blocks, inp.shape[1]
+    s = _strided(scale, num_groups)
+    a = _strided(amax, num_groups, writable=True)
+    args.scale, args.scale_stride = s.ptr, s.stride
+    args.amax, args.amax_stride = a.ptr, a.stride
+    args.out_format = _fp8_code(out.dtype)
+    check(lib.fp8gmm_blocked_cast(ctypes.byref(args), _stream()), "blocked_cast")
+    if a.scatter:
+        a.scatter()
+
+
+def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None):
     args = GemmArgs()
     args.a, args.b, args.c = a.data_ptr(), b3.data_ptr(), c.data_ptr()
     ms, keep = _i64_array(m_sizes)
@@ -301,6 +336,10 @@ def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax):
     args.act_out = _ptr(act_out)
     args.act_scale, args.act_scale_stride = sc.ptr, sc.stride
     args.act_amax, args.act_amax_stride = amax.ptr, amax.stride
+    if c_row_map is not None:
+        _require(c_row_map.is_cuda and c_row_map.dtype == torch.int32 and c_row_map.numel() == a.shape[0],
+                 "c_row_map must be a CUDA int32 tensor with one entry per row of a")
+        args.c_row_map = c_row_map.data_ptr()
     with _Timed(2.0 * a.shape[0] * args.n * args.k):
         check(lib.fp8gmm_grouped_gemm(ctypes.byref(args), _stream()), "fp8_gmm")
     if amax.scatter:
@@ -351,6 +390,7 @@ def fp8_gmm(
     backward=False,
     cutlass=False,
     activation="gelu",
+    c_row_map=None,
 ):
     """Grouped GEMM ``c[rows of g] = (a[rows of g] * sa[g]) (b[g] * sb[g])^T`` in one launch.
 
@@ -361,7 +401,8 @@ def fp8_gmm(
     reference's CUTLASS path runs as a second pass.  With an FP8 ``c`` (or c_dtype) the fused
     activation epilogue runs: ``pre_gelu_out`` gets the bf16 pre-activation, ``c`` the e4m3
     activation scaled by c_scales[g], c_amaxes[g] the amax.  activation="swiglu" expects b = [gate
-    rows | up rows] (N = 2F) and produces a (sum m, F) ``c``.
+    rows | up rows] (N = 2F) and produces a (sum m, F) ``c``.  ``c_row_map`` (CUDA int32, one entry per row
+    of a; plain bf16 output only) makes the epilogue store row r of the product at row c_row_map[r] of c.
     """
     _cuda_2d(a, "a", _FP8)
     _cuda_2d(b, "b", _FP8)
@@ -390,7 +431,7 @@ def fp8_gmm(
     else:
         _require(c.dtype == torch.bfloat16, "fp8_gmm: output must be bfloat16 or float8_e4m3fn")
         _require(pre_gelu_out is None, "fp8_gmm: pre_gelu_out needs an FP8 output")
-        _gemm(a, b, c, group_sizes, G, sa, sb, ACT_NONE, None, _Strided(None, 0), _Strided(None, 0))
+        _gemm(a, b, c, group_sizes, G, sa, sb, ACT_NONE, None, _Strided(None, 0), _Strided(None, 0), c_row_map)
     return c
 
 

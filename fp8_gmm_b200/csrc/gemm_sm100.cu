@@ -65,6 +65,7 @@ struct GemmParams {
   int64_t ldc;     // row pitch of c in elements
   int64_t ld_act;  // row pitch of act_out in bytes
   int* status;
+  const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
   int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
   int mode;
@@ -528,8 +529,9 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quad * 32) << 16);
 
       if (p.activation == FP8GMM_ACT_NONE) {
+        const int64_t dst_row = (p.row_map != nullptr && row_ok) ? static_cast<int64_t>(p.row_map[out_row]) : out_row;
         uint16_t* dst = p.c + (p.mode == kModeWgrad ? static_cast<int64_t>(t.group) * p.m_fixed * p.ldc : 0) +
-                        out_row * p.ldc + t.nt * kBlockN;
+                        dst_row * p.ldc + t.nt * kBlockN;
         for (int c0 = 0; c0 < t.valid_cols; c0 += 32) {
           uint32_t r[32];
           tmem_ld32(taddr + c0, r);
@@ -807,6 +809,9 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.maps = nullptr;
   p.c = static_cast<uint16_t*>(a->c);
   p.act_out = static_cast<uint8_t*>(a->act_out);
+  FP8GMM_CHECK_ARG(a->c_row_map == nullptr || a->activation == FP8GMM_ACT_NONE,
+                   "grouped_gemm: c_row_map is only supported without a fused activation");
+  p.row_map = a->c_row_map;
   p.sa = a->a_scale_inv;
   p.sb = a->b_scale_inv;
   p.sc = a->act_scale;

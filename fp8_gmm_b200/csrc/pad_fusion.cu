@@ -412,4 +412,29 @@ int fp8gmm_grouped_pad_cast_transpose(const fp8gmm_grouped_cast_args* a, void* s
   return run(descs.data(), a->num_groups, mode, a->out_format, stream, "grouped_pad_cast_transpose");
 }
 
+int fp8gmm_blocked_cast(const fp8gmm_blocked_cast_args* a, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(a != nullptr && a->num_blocks >= 0 && a->cols >= 0, "blocked_cast: bad arguments");
+  if (a->num_blocks == 0 || a->cols == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(a->src_start && a->dst_start && a->rows && a->group, "blocked_cast: NULL block array");
+  FP8GMM_CHECK_ARG(a->in != nullptr && a->out != nullptr, "blocked_cast: NULL tensor");
+  std::vector<fp8gmm_tensor_desc> descs(static_cast<size_t>(a->num_blocks));
+  for (int64_t b = 0; b < a->num_blocks; ++b) {
+    fp8gmm_tensor_desc& t = descs[b];
+    FP8GMM_CHECK_ARG(a->rows[b] >= 0 && a->src_start[b] >= 0 && a->dst_start[b] >= 0 && a->group[b] >= 0,
+                     "blocked_cast: block %lld has a negative field", (long long)b);
+    t.in = static_cast<const char*>(a->in) + a->src_start[b] * a->cols * 2;
+    t.in2 = nullptr;
+    t.out = static_cast<char*>(a->out) + a->dst_start[b] * a->cols;
+    t.out_t = nullptr;
+    t.scale = a->scale ? a->scale + a->group[b] * a->scale_stride : nullptr;
+    t.amax = a->amax ? a->amax + a->group[b] * a->amax_stride : nullptr;
+    t.rows = a->rows[b];
+    t.cols = a->cols;
+    t.padded_rows = a->rows[b];
+  }
+  FP8GMM_CHECK_ARG(a->num_blocks <= INT32_MAX, "blocked_cast: too many blocks");
+  return run(descs.data(), static_cast<int>(a->num_blocks), kCast, a->out_format, stream, "blocked_cast");
+}
+
 }  // extern "C"

@@ -31,6 +31,15 @@ class EpPlan:
     to_expert_major: torch.Tensor    # device int64 (R,): expert-major position i reads source-major row index[i]
     to_source_major: torch.Tensor    # device int64 (R,): inverse permutation
     group: object = None
+    recv_counts: torch.Tensor = None  # CPU int64 (P, E_local)
+
+    def row_permutation(self):
+        """The same permutation in the block form the fused kernels take (backend.RowPermutation): the cast reads the
+        source-major blocks and writes them expert-major, the GEMM epilogues write results back source-major."""
+        from .backend import RowPermutation
+
+        src_start, dst_start, rows, group = permutation_blocks(self.recv_counts)
+        return RowPermutation(src_start, dst_start, rows, group, self.to_expert_major.to(torch.int32))
 
 
 def exchange_counts(group_sizes, group=None):
@@ -73,6 +82,18 @@ def block_permutation(recv_counts):
     return to_expert_major, to_source_major
 
 
+def permutation_blocks(recv_counts):
+    """Block table of the source-major -> expert-major permutation: one block per (source rank, local expert).
+    Returns CPU int64 tensors (src_start, dst_start, rows, group), blocks listed in source-major order."""
+    P, El = recv_counts.shape
+    counts = recv_counts.reshape(-1)
+    src_start = torch.cumsum(counts, 0) - counts
+    em = recv_counts.t().contiguous().reshape(-1)                    # blocks in expert-major order (e, src)
+    em_start = (torch.cumsum(em, 0) - em).reshape(El, P).t().contiguous().reshape(-1)   # back to (src, e) order
+    group = torch.arange(El).repeat(P)
+    return src_start, em_start, counts.clone(), group
+
+
 def make_plan(group_sizes, device, group=None):
     world = dist.get_world_size(group)
     E = group_sizes.numel()
@@ -83,7 +104,7 @@ def make_plan(group_sizes, device, group=None):
     fwd, inv = block_permutation(recv_counts)
     return EpPlan(send_rows=send_rows, recv_rows=recv_rows, local_group_sizes=recv_counts.sum(0).contiguous(),
                   to_expert_major=fwd.to(device, non_blocking=True), to_source_major=inv.to(device, non_blocking=True),
-                  group=group)
+                  group=group, recv_counts=recv_counts)
 
 
 class _AllToAllRows(torch.autograd.Function):
@@ -155,9 +176,12 @@ class ExpertParallelMlp(torch.nn.Module):
         if self.world == 1:
             return self.mlp(input, group_sizes, is_first_microbatch=is_first_microbatch)
         plan = make_plan(group_sizes, input.device, self.group)
-        local = dispatch(input, plan)
-        out = self.mlp(local, plan.local_group_sizes, is_first_microbatch=is_first_microbatch)
-        return combine(out, plan)
+        # the exchange delivers rows source-major; the MLP's casts and GEMM epilogues apply the block permutation to
+        # and from expert-major order themselves, so no gather / scatter pass runs on either side
+        recv = _AllToAllRows.apply(input, plan.send_rows, plan.recv_rows, plan.group)
+        out = self.mlp(recv, plan.local_group_sizes, is_first_microbatch=is_first_microbatch,
+                       row_permutation=plan.row_permutation())
+        return _AllToAllRows.apply(out, plan.recv_rows, plan.send_rows, plan.group)
 
 
 class PeerMonitor:

