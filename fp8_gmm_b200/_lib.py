@@ -73,6 +73,10 @@ class WgradArgs(ctypes.Structure):
     ]
 
 
+class CopyBlock(ctypes.Structure):
+    _fields_ = [("dst", c_vp), ("src", c_vp), ("bytes", ctypes.c_size_t)]
+
+
 # name -> (restype, argtypes); must list every symbol the header declares (tests/test_abi.py checks).
 SYMBOLS = {
     "fp8gmm_version": (ctypes.c_int, []),
@@ -91,7 +95,15 @@ SYMBOLS = {
     "fp8gmm_wgrad_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int]),
     "fp8gmm_grouped_wgrad": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_grouped_wgrad_static": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
+    "fp8gmm_set_gemm_sm_limit": (ctypes.c_int, [ctypes.c_int]),
     "fp8gmm_set_gemm_profile_buffer": (ctypes.c_int, [c_vp, ctypes.c_size_t]),
+    "fp8gmm_peer_alloc": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(c_vp), c_vp]),
+    "fp8gmm_peer_free": (ctypes.c_int, [c_vp]),
+    "fp8gmm_peer_open": (ctypes.c_int, [c_vp, ctypes.POINTER(c_vp)]),
+    "fp8gmm_peer_close": (ctypes.c_int, [c_vp]),
+    "fp8gmm_peer_copy_blocks": (ctypes.c_int, [ctypes.POINTER(CopyBlock), ctypes.c_int, c_vp]),
+    "fp8gmm_peer_signal": (ctypes.c_int, [ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_uint32, c_vp]),
+    "fp8gmm_peer_wait": (ctypes.c_int, [c_vp, ctypes.c_int, ctypes.c_uint32, c_vp]),
     "fp8gmm_delayed_scaling_update": (
         ctypes.c_int,
         [c_fp, c_fp, c_fp, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_int, c_vp],

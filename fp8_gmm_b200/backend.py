@@ -37,6 +37,11 @@ def set_gemm_timings(sink):
     _gemm_timings = sink
 
 
+def set_gemm_sm_limit(sms):
+    """Cap the SMs the persistent GEMM kernels occupy (0 = all); see fp8gmm_set_gemm_sm_limit."""
+    check(lib.fp8gmm_set_gemm_sm_limit(int(sms)), "set_gemm_sm_limit")
+
+
 def launch_count():
     """Kernels launched by the C-ABI library in this process so far."""
     return int(lib.fp8gmm_launch_count())

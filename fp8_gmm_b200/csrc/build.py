@@ -22,6 +22,7 @@ BUILD = os.path.join(HERE, "_build")
 # (reference setup.py:21), which fixes flush-to-zero and the tanh/exp approximations they share with it.
 SOURCES = [
     ("runtime.cu", []),
+    ("peer.cu", []),
     ("pointwise.cu", ["--use_fast_math"]),
     ("pad_fusion.cu", ["--use_fast_math"]),
     ("gemm_sm100.cu", ["--use_fast_math"]),

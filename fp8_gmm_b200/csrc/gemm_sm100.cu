@@ -720,9 +720,15 @@ int prefetch_distance() {
   return e ? atoi(e) : 0;
 }
 
+// Upper bound on the SMs a GEMM launch occupies (fp8gmm_set_gemm_sm_limit; 0 = all).  A persistent grid that
+// fills every SM is delayed as a whole when another kernel (an NCCL exchange on a second stream) holds a few SMs.
+int g_sm_limit = 0;
+
 int launch(GemmParams& p, int ctas, cudaStream_t s) {
   // The attribute is per device and the call is idempotent and cheap, so it is simply repeated.
-  const int workers = sm_count() / ctas;
+  int sms = sm_count();
+  if (g_sm_limit > 0 && g_sm_limit < sms) sms = g_sm_limit;
+  const int workers = sms / ctas > 0 ? sms / ctas : 1;
   const int grid = ctas * (p.total_tiles < workers ? p.total_tiles : workers);
   p.prefetch_kb = prefetch_distance();
   p.profile = (g_profile != nullptr && g_profile_bytes >= static_cast<size_t>(grid) * 8 * sizeof(long long)) ? g_profile : nullptr;
@@ -834,6 +840,11 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
   return launch(p, ctas, static_cast<cudaStream_t>(stream));
+}
+
+int fp8gmm_set_gemm_sm_limit(int sms) {
+  fp8gmm::g_sm_limit = sms > 0 ? sms : 0;
+  return FP8GMM_OK;
 }
 
 int fp8gmm_set_gemm_profile_buffer(void* device_buffer, size_t bytes) {

@@ -159,10 +159,16 @@ class ExpertParallelMlp(torch.nn.Module):
     Returns (rows, hidden) in the same order.  ``world_size == 1`` degenerates to the plain GroupedMlp.
     """
 
-    def __init__(self, in_features, out_features, num_experts, dtype, device="cuda", activation="gelu", group=None):
+    def __init__(self, in_features, out_features, num_experts, dtype, device="cuda", activation="gelu", group=None,
+                 transport="auto", num_chunks=4):
+        """``transport``: "peer" = rows pushed by the copy engines into peer-mapped buffers, pipelined with the GEMMs
+        in ``num_chunks`` chunks of experts (fp8_gmm_b200.ep_peer; one NVSwitch node, NCCL process group);
+        "nccl" = NCCL all-to-all before and after the whole local MLP; "auto" = "peer" on an NCCL group."""
         super().__init__()
         from .grouped_mlp import GroupedMlp
 
+        assert transport in ("auto", "peer", "nccl")
+        self.transport, self.num_chunks = transport, num_chunks
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         assert num_experts % self.world == 0, "the number of experts must be divisible by the number of ranks"
@@ -175,6 +181,13 @@ class ExpertParallelMlp(torch.nn.Module):
             group_sizes = torch.tensor(list(group_sizes), dtype=torch.int64)
         if self.world == 1:
             return self.mlp(input, group_sizes, is_first_microbatch=is_first_microbatch)
+        transport = self.transport
+        if transport == "auto":
+            transport = "peer" if input.is_cuda and dist.get_backend(self.group) == "nccl" else "nccl"
+        if transport == "peer":
+            from . import ep_peer
+
+            return ep_peer.forward(self, input, group_sizes, is_first_microbatch, self.num_chunks)
         plan = make_plan(group_sizes, input.device, self.group)
         # the exchange delivers rows source-major; the MLP's casts and GEMM epilogues apply the block permutation to
         # and from expert-major order themselves, so no gather / scatter pass runs on either side

@@ -1,0 +1,398 @@
+"""Expert parallelism over peer memory: the dispatch / combine exchange pipelined with the grouped MLP.
+
+Where fp8_gmm_b200.ep moves rows with NCCL all-to-all around an unchanged GroupedMlp (exchange, then compute,
+then exchange), this module splits a rank's experts into chunks and overlaps the exchange of one chunk with the
+GEMMs of another:
+
+    copy engines :  D0   D1        C0  D2        C1  D3        C2        C3
+    SMs          :  w-cast   [cast fc1 fc2]0   [cast fc1 fc2]1   [...]2   [...]3
+
+``Dk`` pushes the rows of chunk k's experts from every rank straight into their place in the owner's
+expert-major receive buffer (one device-to-device copy per (destination expert) block, so no permutation kernel
+runs on either side); ``Ck`` pushes chunk k's results back to the rows' home ranks, into the tensor the caller
+gets.  Backward runs the same schedule with the gradient.  The copies run on the copy engines (fp8_gmm_b200.peer),
+so the persistent GEMM kernels keep every SM.  The reference has no counterpart (single GPU; its example permutes
+on one device, reference fp8_gmm/example.py:52-59,85-92); numerics per expert are exactly GroupedMlp's.
+
+The plan arithmetic (PeerPlan) is pure host code and is tested on CPU by simulating the copies.
+"""
+import weakref
+
+import torch
+import torch.distributed as dist
+
+from . import backend
+from .peer import PeerBuffer, PeerChannel
+from .recipe import get_fp8_te_dtype
+from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_sizes, to_torch_dtype
+
+_T, _M = Fp8TensorType, MetaTensorType
+
+
+class PeerPlan:
+    """Row bookkeeping of one exchange, derived from everybody's group sizes.
+
+    counts: CPU int64 (P, E), counts[s, e] = rows of global expert e held by rank s (sorted by expert there).
+    Rank o owns experts [o*El, (o+1)*El).  At the owner rows are expert-major and, inside an expert, ordered by
+    source rank.  Offsets are in rows."""
+
+    def __init__(self, counts, rank, num_chunks):
+        counts = counts.to(torch.int64)
+        self.world, self.num_experts = counts.shape
+        self.rank = rank
+        P, E = self.world, self.num_experts
+        assert E % P == 0
+        El = self.experts_local = E // P
+        self.counts = counts
+        zero = torch.zeros(P, 1, dtype=torch.int64)
+        self.send_off = torch.cat([zero, torch.cumsum(counts, 1)], 1)                    # (P, E+1)
+        by_owner = counts.reshape(P, P, El).permute(1, 2, 0).contiguous()               # (owner, j, src)
+        rows_local = by_owner.sum(2)                                                     # (owner, j)
+        self.exp_off = torch.cat([zero, torch.cumsum(rows_local, 1)], 1)                # (owner, El+1)
+        within = torch.cumsum(by_owner, 2) - by_owner                                   # exclusive over src
+        self.blk_off = self.exp_off[:, :El, None] + within                              # (owner, j, src)
+        self.by_owner = by_owner
+        self.local_sizes = rows_local[rank].tolist()
+        self.rows_local_max = int(rows_local.sum(1).max())
+        self.rows_own = int(counts[rank].sum())
+        self.rows_own_max = int(counts.sum(1).max())
+        C = max(1, min(num_chunks, El))
+        bounds = [round(i * El / C) for i in range(C + 1)]
+        self.chunks = [(bounds[i], bounds[i + 1]) for i in range(C) if bounds[i + 1] > bounds[i]]
+        self._lists = {}
+
+    def _peer_order(self):
+        # staggered so that at any moment every receiver is written by a different sender
+        return [(self.rank + i) % self.world for i in range(1, self.world + 1)]
+
+    def dispatch_blocks(self, chunk):
+        """(owner, dst_row at the owner, src_row here, rows) for the rows this rank sends for one chunk of experts."""
+        key = ("d", chunk)
+        if key not in self._lists:
+            j0, j1 = chunk
+            El, r = self.experts_local, self.rank
+            out = []
+            for o in self._peer_order():
+                for j in range(j0, j1):
+                    n = int(self.counts[r, o * El + j])
+                    if n:
+                        out.append((o, int(self.blk_off[o, j, r]), int(self.send_off[r, o * El + j]), n))
+            self._lists[key] = out
+        return self._lists[key]
+
+    def combine_blocks(self, chunk):
+        """(home rank, dst_row at home, src_row here, rows) for the result rows this rank returns for one chunk."""
+        key = ("c", chunk)
+        if key not in self._lists:
+            j0, j1 = chunk
+            El, r = self.experts_local, self.rank
+            out = []
+            for s in self._peer_order():
+                for j in range(j0, j1):
+                    n = int(self.counts[s, r * El + j])
+                    if n:
+                        out.append((s, int(self.send_off[s, r * El + j]), int(self.blk_off[r, j, s]), n))
+            self._lists[key] = out
+        return self._lists[key]
+
+
+class _Pool:
+    """Receive buffers for combined results.  A buffer is handed to the caller as a tensor and comes back when that
+    tensor dies.  Buffers are allocated collectively, so index i names the same allocation round on every rank."""
+
+    def __init__(self, device, group):
+        self.device, self.group = device, group
+        self.buffers, self.free = [], []
+
+    def pick(self, nbytes):
+        for i in self.free:
+            if self.buffers[i].nbytes >= nbytes:
+                self.free.remove(i)
+                return i
+        return -1
+
+    def grow(self, nbytes):
+        self.buffers.append(PeerBuffer(nbytes, self.device, self.group))
+        return len(self.buffers) - 1
+
+    def release(self, i):
+        self.free.append(i)
+
+
+class EpContext:
+    """Per (device, group) transport state shared by all ExpertParallelMlp modules: the channel (side stream and
+    sequence numbers), the receive buffer for dispatched rows and the pool of result buffers."""
+
+    _instances = {}
+
+    @classmethod
+    def get(cls, device, group=None):
+        key = (device.index, id(group))
+        if key not in cls._instances:
+            cls._instances[key] = cls(device, group)
+        return cls._instances[key]
+
+    def __init__(self, device, group):
+        self.device, self.group = device, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.channel = PeerChannel(device, group)
+        self.pool = _Pool(device, group)
+        self.recv = None
+
+    def plan(self, group_sizes, row_bytes, num_chunks, want_grad_buffer):
+        """One small all-gather: everybody's group sizes plus the result buffers each rank picked.  The gather also
+        orders this step's pushes after every rank's previous use of the buffers they land in."""
+        E = group_sizes.numel()
+        own_bytes = int(group_sizes.sum()) * row_bytes
+        pool = self.pool
+        out_id = pool.pick(own_bytes)
+        gi_id = pool.pick(own_bytes) if want_grad_buffer else -2
+        meta = torch.cat([group_sizes.to(torch.int64), torch.tensor([out_id, gi_id], dtype=torch.int64)])
+        mine = meta.to(self.device, non_blocking=True)
+        gathered = torch.empty(self.world, E + 2, dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(gathered, mine, group=self.group)
+        gathered = gathered.cpu()
+        plan = PeerPlan(gathered[:, :E].contiguous(), self.rank, num_chunks)
+        # collective growth: everybody allocates as many new result buffers as the neediest rank asked for
+        missing = int((gathered[:, E:] == -1).sum(1).max())
+        new_ids = [pool.grow(int(plan.rows_own_max * 1.25) * row_bytes + 256) for _ in range(missing)]
+        ids = []
+        for i in (out_id, gi_id):
+            if i == -1:
+                i = new_ids.pop(0)
+            ids.append(i)
+        for i in new_ids:
+            pool.release(i)
+        out_id, gi_id = ids
+        peer_out = gathered[:, E].tolist()
+        peer_gi = gathered[:, E + 1].tolist()
+        # a rank that asked for new buffers takes them in the same order as above: reconstruct its choice
+        n_before = len(pool.buffers) - missing
+        def resolve(o, g):
+            fresh = list(range(n_before, n_before + missing))
+            res = []
+            for i in (o, g):
+                res.append(fresh.pop(0) if i == -1 else i)
+            return res
+        plan.out_ids, plan.gi_ids = zip(*[resolve(o, g) for o, g in zip(peer_out, peer_gi)])
+        need = plan.rows_local_max * row_bytes
+        if self.recv is None or self.recv.nbytes < need:
+            # every rank sees the same sizes, so all of them take this branch together
+            if self.recv is not None:
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group=self.group)
+                self.recv.close()
+            self.recv = PeerBuffer(int(plan.rows_local_max * 1.25) * row_bytes + 256, self.device, self.group)
+        return plan
+
+    def result_tensor(self, buf_id, rows, cols):
+        buf = self.pool.buffers[buf_id]
+        pool = weakref.ref(self.pool)
+
+        def back():
+            p = pool()
+            if p is not None:
+                p.release(buf_id)
+
+        return buf.tensor((rows, cols), torch.bfloat16, on_release=back)
+
+
+def _cast_weight(weight, fp8_dtype, with_transpose, scale, amax):
+    g, n, k = weight.shape
+    w_fp8 = torch.empty(weight.shape, dtype=fp8_dtype, device=weight.device)
+    w_t = torch.empty(g, k, n, dtype=fp8_dtype, device=weight.device) if with_transpose else None
+    offs = [i * n for i in range(g + 1)]
+    backend.grouped_cast_transpose(weight.view(g * n, k), offs, w_fp8, w_t, offs, scale, amax)
+    return w_fp8, w_t
+
+
+def _rel(offsets, j0, j1):
+    base = offsets[j0]
+    return [o - base for o in offsets[j0:j1 + 1]]
+
+
+class _PeerEpMlp(torch.autograd.Function):
+    """fc1 -> activation -> fc2 over this rank's experts with the row exchange pipelined chunk by chunk."""
+
+    @staticmethod
+    def forward(ctx, x, fc1_weight, fc2_weight, st):
+        mlp, plan, ectx = st["mlp"], st["plan"], st["ctx"]
+        ch = ectx.channel
+        fp8_meta, activation = mlp.fp8_meta, mlp.activation
+        grad_on = st["grad_enabled"]
+        need_wgrad = grad_on and fc1_weight.requires_grad
+        need_dgrad = grad_on and x.requires_grad
+        El = plan.experts_local
+        _, padded, cumsums, padded_cumsums = cumsum_group_sizes(plan.local_sizes, need_padding=need_wgrad)
+        offs = padded_cumsums if padded else cumsums
+        rows = cumsums[-1]
+        metas = Fp8MetaWrapper(El, fp8_meta)
+        fdt = to_torch_dtype(get_fp8_te_dtype(fp8_meta["recipe"], fprop_tensor=True))
+        x = x.contiguous()
+        hidden = x.shape[1]
+        row_bytes = hidden * 2
+        fc1_out = fc1_weight.shape[1]
+        ffn = fc1_out // 2 if activation == "swiglu" else fc1_out
+        dev = x.device
+        sizes_cpu = torch.tensor(plan.local_sizes, dtype=torch.int64)
+
+        recv_ptrs = ectx.recv.ptrs
+        x_ptr = x.data_ptr()
+
+        def dispatch(chunk):
+            return ch.push([(recv_ptrs[o] + d * row_bytes, x_ptr + s * row_bytes, n * row_bytes)
+                            for o, d, s, n in plan.dispatch_blocks(chunk)])
+
+        chunks = plan.chunks
+        seq = [None] * len(chunks)
+        seq[0] = dispatch(chunks[0])
+        # the weight casts run while the first rows are on their way
+        ms = metas.get_meta_strided
+        fc1_w_fp8, fc1_w_t = _cast_weight(fc1_weight, fdt, need_dgrad, ms(_T.kWeightGroup1, _M.kScale), ms(_T.kWeightGroup1, _M.kAmax))
+        fc2_w_fp8, fc2_w_t = _cast_weight(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
+                                          ms(_T.kWeightGroup2, _M.kAmax))
+        recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
+        input_fp8 = torch.empty(rows, hidden, dtype=fdt, device=dev)
+        input_t_fp8 = torch.empty(offs[-1], hidden, dtype=fdt, device=dev) if need_wgrad else None
+        pre_act = torch.empty(rows, fc1_out, dtype=torch.bfloat16, device=dev)
+        act_fp8 = torch.empty(rows, ffn, dtype=fdt, device=dev)
+        out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+        out = ectx.result_tensor(plan.out_ids[plan.rank], plan.rows_own, hidden)
+        out_ptrs = [ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)]
+        last = None
+        for c, (j0, j1) in enumerate(chunks):
+            if c + 1 < len(chunks):
+                seq[c + 1] = dispatch(chunks[c + 1])
+            ch.wait(seq[c])
+            r0, r1 = cumsums[j0], cumsums[j1]
+            if r1 > r0:
+                backend.grouped_cast_transpose(
+                    recv[r0:r1], _rel(cumsums, j0, j1), input_fp8[r0:r1],
+                    input_t_fp8[offs[j0]:offs[j1]] if need_wgrad else None, _rel(offs, j0, j1),
+                    ms(_T.kInputGroup1, _M.kScale, j0), ms(_T.kInputGroup1, _M.kAmax, j0))
+                backend.fp8_gmm(
+                    input_fp8[r0:r1], fc1_w_fp8[j0:j1], sizes_cpu[j0:j1],
+                    ms(_T.kInputGroup1, _M.kScaleInv, j0), ms(_T.kWeightGroup1, _M.kScaleInv, j0),
+                    c=act_fp8[r0:r1], pre_gelu_out=pre_act[r0:r1],
+                    c_scales=ms(_T.kInputGroup2, _M.kScale, j0), c_amaxes=ms(_T.kInputGroup2, _M.kAmax, j0),
+                    backward=False, activation=activation)
+                backend.fp8_gmm(
+                    act_fp8[r0:r1], fc2_w_fp8[j0:j1], sizes_cpu[j0:j1],
+                    ms(_T.kInputGroup2, _M.kScaleInv, j0), ms(_T.kWeightGroup2, _M.kScaleInv, j0),
+                    c=out_local[r0:r1], backward=False)
+            o_ptr = out_local.data_ptr()
+            last = ch.push([(out_ptrs[s] + d * row_bytes, o_ptr + l * row_bytes, n * row_bytes)
+                            for s, d, l, n in plan.combine_blocks((j0, j1))])
+        ch.wait(last)
+        if grad_on:
+            # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
+            # backward never runs
+            ctx.gi = ectx.result_tensor(plan.gi_ids[plan.rank], plan.rows_own, hidden) if need_dgrad else None
+            ctx.save_for_backward(input_t_fp8, fc1_w_t, fc2_w_t, pre_act, act_fp8 if need_wgrad else None)
+            metas.set_forward_scale_inv_cloned()
+            ctx.metas, ctx.st = metas, st
+            ctx.cumsums, ctx.offs, ctx.sizes_cpu = cumsums, offs, sizes_cpu
+            ctx.fc1_shape, ctx.fc2_shape = fc1_weight.shape, fc2_weight.shape
+            ctx.need_wgrad, ctx.need_dgrad = need_wgrad, need_dgrad
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        input_t_fp8, fc1_w_t, fc2_w_t, pre_act, act_fp8 = ctx.saved_tensors
+        st, metas, cumsums, offs, sizes_cpu = ctx.st, ctx.metas, ctx.cumsums, ctx.offs, ctx.sizes_cpu
+        mlp, plan, ectx = st["mlp"], st["plan"], st["ctx"]
+        ch = ectx.channel
+        fp8_meta, activation = mlp.fp8_meta, mlp.activation
+        fp8_meta["prepare_backward"]()
+        gdt = to_torch_dtype(get_fp8_te_dtype(fp8_meta["recipe"], fprop_tensor=False))
+        dy = grad_out.contiguous()
+        El, fc1_out, hidden = ctx.fc1_shape
+        ffn = ctx.fc2_shape[2]
+        row_bytes = hidden * 2
+        rows = cumsums[-1]
+        dev = dy.device
+        wgrad, dgrad = ctx.need_wgrad, ctx.need_dgrad
+        ms = metas.get_meta_strided
+
+        recv_ptrs = ectx.recv.ptrs
+        dy_ptr = dy.data_ptr()
+
+        def dispatch(chunk):
+            return ch.push([(recv_ptrs[o] + d * row_bytes, dy_ptr + s * row_bytes, n * row_bytes)
+                            for o, d, s, n in plan.dispatch_blocks(chunk)])
+
+        chunks = plan.chunks
+        seq = [None] * len(chunks)
+        seq[0] = dispatch(chunks[0])
+        recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
+        grad_out_fp8 = torch.empty(rows, hidden, dtype=gdt, device=dev)
+        grad_out_t = torch.empty(offs[-1], hidden, dtype=gdt, device=dev) if wgrad else None
+        act_t = torch.empty(offs[-1], ffn, dtype=act_fp8.dtype, device=dev) if wgrad else None
+        grad_pre_fp8 = torch.empty(rows, fc1_out, dtype=gdt, device=dev)
+        grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=gdt, device=dev) if wgrad else None
+        grad_fc1 = torch.empty(ctx.fc1_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
+        grad_fc2 = torch.empty(ctx.fc2_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
+        gi_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev) if dgrad else None
+        gi = ctx.gi
+        ctx.gi = None
+        if dgrad:
+            assert min(plan.gi_ids) >= 0, "input.requires_grad must agree on all ranks"
+            gi_ptrs = [ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)]
+        last = None
+        for c, (j0, j1) in enumerate(chunks):
+            if c + 1 < len(chunks):
+                seq[c + 1] = dispatch(chunks[c + 1])
+            r0, r1 = cumsums[j0], cumsums[j1]
+            t0, t1 = offs[j0], offs[j1]
+            live = r1 > r0
+            if live and wgrad:
+                # needs no gradient rows: runs while they are still on their way
+                backend.grouped_cast_transpose(act_fp8[r0:r1], _rel(cumsums, j0, j1), None, act_t[t0:t1], _rel(offs, j0, j1),
+                                               None, None)
+            ch.wait(seq[c])
+            if live:
+                backend.grouped_cast_transpose(
+                    recv[r0:r1], _rel(cumsums, j0, j1), grad_out_fp8[r0:r1], grad_out_t[t0:t1] if wgrad else None,
+                    _rel(offs, j0, j1), ms(_T.kGradOutputGroup1, _M.kScale, j0), ms(_T.kGradOutputGroup1, _M.kAmax, j0))
+                dy_si = ms(_T.kGradOutputGroup1, _M.kScaleInv, j0)
+                if wgrad:
+                    backend.grouped_wgrad(grad_out_t[t0:t1], act_t[t0:t1], _rel(offs, j0, j1), hidden, ffn, dy_si,
+                                          ms(_T.kForwardInputGroup2, _M.kScaleInv, j0), c=grad_fc2[j0:j1])
+                grad_act = backend.fp8_gmm(grad_out_fp8[r0:r1], fc2_w_t[j0:j1], sizes_cpu[j0:j1], dy_si,
+                                           ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), backward=True)
+                backend.grouped_cast_transpose(
+                    grad_act, _rel(cumsums, j0, j1), grad_pre_fp8[r0:r1], grad_pre_t[t0:t1] if wgrad else None,
+                    _rel(offs, j0, j1), ms(_T.kGradOutputGroup2, _M.kScale, j0), ms(_T.kGradOutputGroup2, _M.kAmax, j0),
+                    in2=pre_act[r0:r1], activation=activation)
+                dpre_si = ms(_T.kGradOutputGroup2, _M.kScaleInv, j0)
+                if dgrad:
+                    backend.fp8_gmm(grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], sizes_cpu[j0:j1], dpre_si,
+                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=gi_local[r0:r1], backward=True)
+            elif wgrad:
+                grad_fc1[j0:j1].zero_()
+                grad_fc2[j0:j1].zero_()
+            if dgrad:
+                g_ptr = gi_local.data_ptr()
+                last = ch.push([(gi_ptrs[s] + d * row_bytes, g_ptr + l * row_bytes, n * row_bytes)
+                                for s, d, l, n in plan.combine_blocks((j0, j1))])
+            else:
+                last = ch.push([])
+            if live and wgrad:
+                backend.grouped_wgrad(grad_pre_t[t0:t1], input_t_fp8[t0:t1], _rel(offs, j0, j1), fc1_out, hidden, dpre_si,
+                                      ms(_T.kForwardInputGroup1, _M.kScaleInv, j0), c=grad_fc1[j0:j1])
+        ch.wait(last)
+        return gi, grad_fc1, grad_fc2, None
+
+
+def forward(module, input, group_sizes, is_first_microbatch, num_chunks):
+    """ExpertParallelMlp.forward over the peer-memory transport."""
+    mlp = module.mlp
+    ectx = EpContext.get(input.device, module.group)
+    grad_on = torch.is_grad_enabled()
+    want_gi = grad_on and input.requires_grad
+    plan = ectx.plan(group_sizes, input.shape[1] * 2, num_chunks, want_gi)
+    st = {"mlp": mlp, "plan": plan, "ctx": ectx, "grad_enabled": grad_on}
+    with mlp.prepare_forward(input, is_first_microbatch, mlp.num_groups * 2):
+        if grad_on:
+            return _PeerEpMlp.apply(input, mlp.fc1_weight, mlp.fc2_weight, st)
+        return _PeerEpMlp.forward(None, input, mlp.fc1_weight, mlp.fc2_weight, st)

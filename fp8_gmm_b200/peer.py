@@ -1,0 +1,130 @@
+"""Peer-memory transport between the ranks of one NVSwitch node (one process per GPU).
+
+Used by fp8_gmm_b200.ep for the dispatch / combine row exchange; the reference has nothing comparable (it is
+single-GPU apart from one all-reduce, reference fp8_gmm/grouped_mlp.py:300-303).  Every rank allocates receive
+buffers through the C ABI (cudaMalloc + CUDA IPC export), all ranks map each other's buffers once, and from then
+on rows move as device-to-device copies on a side stream: the copy engines push them over NVLink while the SMs
+keep running GEMMs.  A 32-bit sequence number per (receiver, sender) pair, written after the sender's copies
+and awaited by a one-warp kernel on the receiver's compute stream, says when a round of copies has landed.
+``torch.distributed`` is used only at set-up (to hand the IPC handles round) -- nothing on the data path.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ._lib import CopyBlock, check, lib
+
+_HANDLE_BYTES = 64
+
+
+class _Span:
+    """Minimal __cuda_array_interface__ holder so torch can view foreign device memory without copying.
+    ``on_release`` runs when the last tensor made from it is gone."""
+
+    def __init__(self, ptr, nbytes, on_release=None):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+        self._on_release = on_release
+
+    def __del__(self):
+        if self._on_release is not None:
+            try:
+                self._on_release()
+            except Exception:  # interpreter shutdown
+                pass
+
+
+def as_tensor(ptr, shape, dtype, device, on_release=None):
+    """Torch tensor over ``ptr`` (device memory not owned by torch's allocator)."""
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    nbytes = numel * torch.empty((), dtype=dtype).element_size()
+    if nbytes == 0:
+        return torch.empty(shape, dtype=dtype, device=device)
+    flat = torch.as_tensor(_Span(ptr, nbytes, on_release), device=device)
+    return flat.view(dtype).view(*shape)
+
+
+class PeerBuffer:
+    """One device buffer per rank, each mapped by every other rank.  Collective: all ranks of ``group`` must
+    create their buffers in the same order.  ``ptrs[r]`` is rank r's buffer as seen from this process."""
+
+    def __init__(self, nbytes, device, group=None):
+        self.group, self.device, self.nbytes = group, device, int(nbytes)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(_HANDLE_BYTES)
+        with torch.cuda.device(device):
+            check(lib.fp8gmm_peer_alloc(self.nbytes, ctypes.byref(ptr), handle), "peer_alloc")
+        self.local = ptr.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self.local)
+                continue
+            p = ctypes.c_void_p()
+            with torch.cuda.device(device):
+                check(lib.fp8gmm_peer_open(ctypes.create_string_buffer(h, _HANDLE_BYTES), ctypes.byref(p)), "peer_open")
+            self.ptrs.append(p.value)
+        self._closed = False
+
+    def tensor(self, shape, dtype, byte_offset=0, on_release=None):
+        return as_tensor(self.local + byte_offset, shape, dtype, self.device, on_release)
+
+    def close(self):
+        """Unmaps the peers' buffers and frees the local one.  Collective in spirit: call it on every rank once
+        no rank still copies into these buffers (e.g. after a barrier)."""
+        if self._closed:
+            return
+        self._closed = True
+        with torch.cuda.device(self.device):
+            for r, p in enumerate(self.ptrs):
+                if r != self.rank:
+                    lib.fp8gmm_peer_close(p)
+            lib.fp8gmm_peer_free(self.local)
+
+
+class PeerChannel:
+    """Side stream + sequence numbers of one group of ranks.
+
+    ``push(blocks)`` enqueues copies on the side stream (after whatever the compute stream has enqueued so far)
+    and then announces a new sequence number to every rank; ``wait(seq)`` makes the compute stream wait until every
+    rank's copies up to ``seq`` have landed here.  All ranks must call ``push`` the same number of times in the
+    same order -- a rank with nothing to send still pushes an empty round."""
+
+    def __init__(self, device, group=None):
+        self.group, self.device = group, device
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        assert self.world <= 64
+        self.flags = PeerBuffer(4096, device, group)          # word s of rank r's page: rounds completed by sender s
+        self.stream = torch.cuda.Stream(device=device)
+        self.seq = 0
+        arr = (ctypes.c_void_p * self.world)()
+        for r in range(self.world):
+            arr[r] = self.flags.ptrs[r] + 4 * self.rank       # my word in rank r's page
+        self._signal_targets = arr
+
+    def push(self, blocks, after_compute=True):
+        """blocks: iterable of (dst_ptr, src_ptr, nbytes).  Returns the sequence number of this round."""
+        blocks = [b for b in blocks if b[2] > 0]
+        arr = (CopyBlock * max(len(blocks), 1))()
+        for i, (dst, src, nbytes) in enumerate(blocks):
+            arr[i].dst, arr[i].src, arr[i].bytes = dst, src, nbytes
+        self.seq = (self.seq + 1) & 0xFFFFFFFF
+        if after_compute:
+            self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        s = self.stream.cuda_stream
+        check(lib.fp8gmm_peer_copy_blocks(arr, len(blocks), s), "peer_copy_blocks")
+        check(lib.fp8gmm_peer_signal(self._signal_targets, self.world, self.seq, s), "peer_signal")
+        return self.seq
+
+    def wait(self, seq):
+        """Compute stream waits for round ``seq`` of every sender (bounded on the device; see fp8gmm_peer_wait)."""
+        check(lib.fp8gmm_peer_wait(self.flags.local, self.world, seq, torch.cuda.current_stream(self.device).cuda_stream),
+              "peer_wait")
+
+    def close(self):
+        self.flags.close()

@@ -133,10 +133,10 @@ class Fp8MetaWrapper:
         t, first, stride = self._resolve(fp8_tensor_type, meta_tensor_type)
         return [t[first + i * stride] for i in range(self._num_groups)]
 
-    def get_meta_strided(self, fp8_tensor_type, meta_tensor_type):
-        """(1-D view starting at group 0's slot, stride): the same slots without building G views.
+    def get_meta_strided(self, fp8_tensor_type, meta_tensor_type, group_start=0):
+        """(1-D view starting at the slot of group ``group_start``, stride): the same slots without building G views.
 
         This is what the grouped C-ABI entry points consume (``base[g * stride]``).
         """
         t, first, stride = self._resolve(fp8_tensor_type, meta_tensor_type)
-        return t[first:], stride
+        return t[first + group_start * stride:], stride

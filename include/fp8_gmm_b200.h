@@ -280,6 +280,14 @@ size_t fp8gmm_wgrad_workspace_bytes(int num_groups);
 int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* args, void* stream);
 
 /*
+ * Limits the number of SMs the (persistent) grouped-GEMM kernels occupy from now on; 0 restores "all SMs".
+ * Process-wide.  Used when a collective runs concurrently on another stream (expert parallelism): a grid that
+ * fills every SM would otherwise wait as a whole for the SMs the collective's kernel holds.  No counterpart in
+ * the reference.
+ */
+int fp8gmm_set_gemm_sm_limit(int sms);
+
+/*
  * Profiling aid with no counterpart in the reference: while a device buffer of at least
  * 8 * sizeof(int64) * (number of CTAs launched, at most 148) bytes is installed, every grouped-GEMM CTA
  * writes its stall counters in SM clock cycles to buffer[cta*8 + i]:
@@ -302,6 +310,43 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* args, void* stream);
  * ---------------------------------------------------------------------------------------------- */
 int fp8gmm_delayed_scaling_update(float* amax_history, float* scale, float* scale_inv, int history_len, int n,
                                   float fp8_max, float margin, int algo, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Peer-memory transport for the expert-parallel row exchange (dispatch / combine between the GPUs of one
+ * NVSwitch node).  No counterpart in the reference, which is single-GPU apart from one all-reduce
+ * (reference fp8_gmm/grouped_mlp.py:300-303) and permutes rows on one device (fp8_gmm/example.py:52-59).
+ * Rows move as device-to-device copies executed by the copy engines (no SM is taken from a GEMM running
+ * at the same time); completion is announced through per-(receiver, sender) 32-bit sequence numbers.
+ * ---------------------------------------------------------------------------------------------- */
+#define FP8GMM_PEER_HANDLE_BYTES 64
+
+/* cudaMalloc of `bytes` on the current device plus its CUDA IPC handle (FP8GMM_PEER_HANDLE_BYTES bytes written
+ * to `handle`), to be sent to the other ranks.  The first 4 KiB are zeroed (sequence-number pages start at 0). */
+int fp8gmm_peer_alloc(size_t bytes, void** ptr, void* handle);
+int fp8gmm_peer_free(void* ptr);
+/* Maps a buffer another process of this node exported with fp8gmm_peer_alloc; `*ptr` is valid in this process
+ * until fp8gmm_peer_close.  Peer access between the two devices is enabled on first use. */
+int fp8gmm_peer_open(const void* handle, void** ptr);
+int fp8gmm_peer_close(void* ptr);
+
+typedef struct {
+  void* dst;       /* local or peer-mapped device address */
+  const void* src; /* local or peer-mapped device address */
+  size_t bytes;    /* 0 = skipped */
+} fp8gmm_copy_block;
+
+/* Enqueues one device-to-device copy per block on `stream`, in order. */
+int fp8gmm_peer_copy_blocks(const fp8gmm_copy_block* blocks, int count, void* stream);
+
+/* One-warp kernel on `stream`: stores `value` to each of the `count` (<= 64) addresses in `flags` (host array of
+ * device addresses, normally one word in every peer's memory; NULL entries are skipped) with system-scope
+ * ordering after everything the stream did before. */
+int fp8gmm_peer_signal(uint32_t* const* flags, int count, uint32_t value, void* stream);
+
+/* One-warp kernel on `stream`: returns once all of flags[0..count) (device array in local memory, count <= 64) have
+ * reached `value` (compared modulo 2^32).  The wait is bounded (about two seconds); when it runs out the kernel
+ * sets a bit in the device status word (see fp8gmm_device_status) and returns. */
+int fp8gmm_peer_wait(const uint32_t* flags, int count, uint32_t value, void* stream);
 
 #ifdef __cplusplus
 }

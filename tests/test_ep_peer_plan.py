@@ -1,0 +1,65 @@
+"""CPU: the row bookkeeping of the peer-memory exchange (fp8_gmm_b200.ep_peer.PeerPlan).  The device copies are
+simulated with numpy: every rank's dispatch blocks are applied to per-rank receive arrays, the "experts" tag the
+rows, and the combine blocks must bring every row back to where it started."""
+import numpy as np
+import pytest
+import torch
+
+from fp8_gmm_b200.ep_peer import PeerPlan
+
+
+def _counts(P, E, seed, zeros=True):
+    g = torch.Generator().manual_seed(seed)
+    c = torch.randint(0, 9, (P, E), generator=g)
+    if zeros:
+        c[0, 1] = 0
+        c[:, E - 1] = 0  # an expert nobody routes to
+    return c
+
+
+@pytest.mark.parametrize("P,E,chunks", [(2, 6, 3), (4, 8, 2), (8, 16, 4), (2, 2, 4), (3, 9, 1)])
+def test_dispatch_then_combine_is_the_identity(P, E, chunks):
+    counts = _counts(P, E, seed=P * 100 + E)
+    plans = [PeerPlan(counts, r, chunks) for r in range(P)]
+    El = E // P
+    # payload of a row: (home rank, home row, global expert)
+    x = []
+    for s in range(P):
+        expert = np.repeat(np.arange(E), counts[s].numpy())
+        x.append(np.stack([np.full(expert.shape, s), np.arange(expert.size), expert], 1))
+    recv = [np.full((int(sum(plans[o].local_sizes)), 3), -1) for o in range(P)]
+    for chunk_index in range(len(plans[0].chunks)):
+        for s in range(P):
+            for o, d, src, n in plans[s].dispatch_blocks(plans[s].chunks[chunk_index]):
+                assert (recv[o][d:d + n] == -1).all(), "two blocks overlap at the owner"
+                recv[o][d:d + n] = x[s][src:src + n]
+    for o in range(P):
+        assert (recv[o] != -1).all(), "a row of the receive buffer was never written"
+        # expert-major, and inside an expert ordered by source rank then source row
+        local_expert = recv[o][:, 2] - o * El
+        assert ((local_expert >= 0) & (local_expert < El)).all()
+        key = local_expert * 10**8 + recv[o][:, 0] * 10**5 + recv[o][:, 1]
+        assert (np.diff(key) > 0).all()
+        assert np.bincount(local_expert, minlength=El).tolist() == plans[o].local_sizes
+    back = [np.full_like(x[s], -1) for s in range(P)]
+    for o in range(P):
+        for chunk in plans[o].chunks:
+            for s, d, src, n in plans[o].combine_blocks(chunk):
+                back[s][d:d + n] = recv[o][src:src + n]
+    for s in range(P):
+        assert (back[s] == x[s]).all()
+
+
+def test_chunks_cover_the_local_experts_once():
+    counts = _counts(4, 20, seed=1, zeros=False)
+    for chunks in (1, 2, 3, 5, 8):
+        plan = PeerPlan(counts, 1, chunks)
+        covered = [j for j0, j1 in plan.chunks for j in range(j0, j1)]
+        assert covered == list(range(5))
+        assert len(plan.chunks) == min(chunks, 5)
+
+
+def test_staggered_peer_order():
+    counts = _counts(4, 8, seed=3, zeros=False)
+    firsts = [PeerPlan(counts, r, 1).dispatch_blocks((0, 2))[0][0] for r in range(4)]
+    assert sorted(firsts) == [0, 1, 2, 3], "every rank must start with a different destination"

@@ -18,7 +18,7 @@ def _sizes(rank):
     return s
 
 
-def _worker(rank, port, errq):
+def _worker(rank, port, errq, transport):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         dev = torch.device("cuda", rank)
@@ -37,7 +37,8 @@ def _worker(rank, port, errq):
             xs.append(torch.randn(n, H, generator=gr).to(torch.bfloat16))
             dys.append(torch.randn(n, H, generator=gr).to(torch.bfloat16))
         El = E // WORLD
-        model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu")
+        model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu", transport=transport,
+                                     num_chunks=2)
         with torch.no_grad():
             model.mlp.fc1_weight.copy_(w1[rank * El:(rank + 1) * El])
             model.mlp.fc2_weight.copy_(w2[rank * El:(rank + 1) * El])
@@ -46,6 +47,18 @@ def _worker(rank, port, errq):
             out = model(x, _sizes(rank))
         out.backward(dys[rank].to(dev))
         fg.backend.device_status()
+        if transport == "peer":
+            # a second step reuses the receive buffers and the result pool: same inputs, same state -> same results
+            first = (out.detach().clone(), x.grad.clone(), model.mlp.fc1_weight.grad.clone())
+            del out
+            x.grad, model.mlp.fc1_weight.grad, model.mlp.fc2_weight.grad = None, None, None
+            model.mlp.fp8_meta_tensors_initialized = False   # restart delayed scaling so step 2 repeats step 1
+            with fg.fp8_autocast(enabled=True):
+                out = model(x, _sizes(rank))
+            out.backward(dys[rank].to(dev))
+            fg.backend.device_status()
+            assert torch.equal(out, first[0]) and torch.equal(x.grad, first[1])
+            assert torch.equal(model.mlp.fc1_weight.grad, first[2])
         # single-GPU reference on this rank: all experts, rows of both source ranks interleaved expert-major
         ref = fg.GroupedMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu")
         with torch.no_grad():
@@ -80,13 +93,14 @@ def _worker(rank, port, errq):
         raise
 
 
-def test_expert_parallel_matches_single_gpu(cuda):
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+def test_expert_parallel_matches_single_gpu(cuda, transport):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs 2 GPUs")
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
-    port = 29900 + os.getpid() % 90
-    procs = [ctx.Process(target=_worker, args=(r, port, errq)) for r in range(WORLD)]
+    port = 29900 + os.getpid() % 90 + (100 if transport == "peer" else 0)
+    procs = [ctx.Process(target=_worker, args=(r, port, errq, transport)) for r in range(WORLD)]
     for p in procs:
         p.start()
     for p in procs:
