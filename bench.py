@@ -53,6 +53,9 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="auto", choices=["auto", "mixtral", "ep"])
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
+                   help="expert-parallel leg: copy-engine pushes into peer memory pipelined with the GEMMs, or NCCL all-to-all")
+    p.add_argument("--ep-chunks", type=int, default=4, help="expert chunks of the peer-transport pipeline")
     return p.parse_args()
 
 
