@@ -25,6 +25,7 @@ N > 1 -> expert parallelism (128 experts split over the ranks, hidden 4096, ffn 
 GPU top-8, all-to-all dispatch/combine over NCCL).
 """
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -87,15 +88,16 @@ def mlp_flops(rows, H, F):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi.  The sampler process starts when the object is
+    created (do that before the warm-up: nvidia-smi needs a moment to come up, longer with eight GPUs); the ``with``
+    block marks the timed region, and only samples stamped inside it are summarised."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.samples, self.proc = index, [], None
-
-    def __enter__(self):
+        self.index, self.raw, self.samples, self.proc = index, [], [], None
+        self.t0 = self.t1 = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
@@ -104,21 +106,32 @@ class ClockSampler:
             self.thread.start()
         except OSError:
             self.proc = None
+
+    def __enter__(self):
+        self.t0 = datetime.datetime.now()
         return self
 
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6 and parts[0].isdigit():
-                self.samples.append(parts)
+            if len(parts) == 7 and parts[1].isdigit():
+                try:
+                    stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                except ValueError:
+                    continue
+                self.raw.append((stamp, parts[1:]))
 
     def __exit__(self, *exc):
+        self.t1 = datetime.datetime.now()
         if self.proc is not None:
+            time.sleep(0.12)  # let the sample that covers the end of the region arrive
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        slack = datetime.timedelta(milliseconds=60)
+        self.samples = [v for t, v in self.raw if self.t0 - slack <= t <= self.t1 + slack]
 
     def summary(self):
         if not self.samples:
@@ -239,6 +252,7 @@ def run_single(args):
         out_host.copy_(out.detach(), non_blocking=True)
         gi_host.copy_(x_dev.grad, non_blocking=True)
 
+    sampler = ClockSampler(dev.index or 0)
     for _ in range(max(args.warmup, 3)):
         step()
     backend.device_status()
@@ -247,7 +261,7 @@ def run_single(args):
     timings = []
     backend.set_gemm_timings(timings)
     launches0 = backend.launch_count()
-    with ClockSampler(dev.index or 0) as clocks:
+    with sampler as clocks:
         secs = timed_steps(step, args.steps)
     launches = backend.launch_count() - launches0
     backend.set_gemm_timings(None)

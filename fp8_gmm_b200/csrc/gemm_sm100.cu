@@ -54,6 +54,7 @@ enum GemmMode { kModeRows = 0, kModeWgrad = 1 };
 struct GemmParams {
   CUtensorMap map_a;          // kModeRows: A (sum m, K)
   CUtensorMap map_b;          // kModeRows: B (G*N, K)
+  CUtensorMap map_c;          // bf16 result (or pre-activation) as a 2-D tensor, box 64 columns x 32 rows, for TMA stores
   const CUtensorMap* maps;    // kModeWgrad: [2g] = A_t,g (N, L_g), [2g+1] = B_t,g (K, L_g)
   uint16_t* c;
   uint8_t* act_out;
@@ -68,6 +69,7 @@ struct GemmParams {
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
   int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
+  int tma_store;       // 1: full 32-row slabs of a tile leave through shared memory + TMA stores (map_c is valid)
   int mode;
   int activation;
   int num_groups;
@@ -145,6 +147,28 @@ __device__ __forceinline__ void prefetch_l2_2d(const CUtensorMap* map, int x, in
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
+
+// ---- TMA store of a staged (32 rows x 128 bytes, SWIZZLE_128B) box -------------------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once at most kPending of this thread's bulk groups still read their shared-memory source.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's generic-proxy shared-memory writes before later async-proxy (TMA) reads of them.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared16(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Byte offset of 16-byte chunk `c` (0..7) of row `r` (0..31) inside a 4 KiB staging box with 128-byte rows in
+// the SWIZZLE_128B pattern the tensor map expects (the box starts on a 1024-byte boundary).
+__device__ __forceinline__ uint32_t staged_chunk(int r, int c) { return static_cast<uint32_t>(r * 128 + ((c ^ (r & 7)) << 4)); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -305,7 +329,8 @@ struct Cfg {
   static constexpr int kBRows = kBlockN / kCtas;              // B rows held by one CTA
   static constexpr int kBBytes = kBRows * kBlockK;
   static constexpr int kStageBytes = kTileABytes + kBBytes;   // 48 KiB (1 CTA) / 32 KiB (pair)
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStagingBytes = 4 * 8192;             // per epilogue warp: two 4 KiB boxes for TMA stores
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -320,7 +345,8 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;  // SWIZZLE_128B atoms need 1024-byte alignment
   uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + kStages * kStageBytes);
+  const uint32_t staging_addr = tiles_addr + kStages * kStageBytes;  // 1024-byte aligned: stages are multiples of 1 KiB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + kStages * kStageBytes + C::kStagingBytes);
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -528,7 +554,45 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quad * 32) << 16);
 
-      if (p.activation == FP8GMM_ACT_NONE) {
+      // A warp whose 32 rows all belong to the tile stages its results in shared memory and lets TMA write
+      // them (full 128-byte lines per row instead of 32 scattered 16-byte stores per instruction).
+      const int tile_cols = p.activation == FP8GMM_ACT_SWIGLU ? kBlockN / 2 : kBlockN;
+      const bool use_tma = p.tma_store != 0 && t.valid_rows - quad * 32 >= 32 && t.valid_cols == tile_cols;
+      const uint32_t stage0 = staging_addr + static_cast<uint32_t>(quad) * 8192u;
+      const int row_coord = static_cast<int>((p.mode == kModeWgrad ? static_cast<int64_t>(t.group) * p.m_fixed : 0) + t.row0) + quad * 32;
+      if (p.activation == FP8GMM_ACT_NONE && use_tma) {
+        const int col_base = t.nt * kBlockN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+          const int half = (c0 >> 5) & 1;
+          const uint32_t box = stage0 + static_cast<uint32_t>((c0 >> 6) & 1) * 4096u;
+          if (half == 0) {
+            // the store issued two boxes ago read this buffer: it must be done reading before we overwrite it
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+          }
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
+            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
+            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
+            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
+            st_shared16(box + staged_chunk(lane, half * 4 + v), o);
+          }
+          if (half == 1) {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&p.map_c, box, col_base + c0 - 32, row_coord);
+              bulk_commit();
+            }
+          }
+        }
+      } else if (p.activation == FP8GMM_ACT_NONE) {
         const int64_t dst_row = (p.row_map != nullptr && row_ok) ? static_cast<int64_t>(p.row_map[out_row]) : out_row;
         uint16_t* dst = p.c + (p.mode == kModeWgrad ? static_cast<int64_t>(t.group) * p.m_fixed * p.ldc : 0) +
                         dst_row * p.ldc + t.nt * kBlockN;
@@ -576,6 +640,58 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     make_uint2(cvt_fp8x4<FP8GMM_E4M3>(g[0] * sc, g[1] * sc, g[2] * sc, g[3] * sc),
                                cvt_fp8x4<FP8GMM_E4M3>(g[4] * sc, g[5] * sc, g[6] * sc, g[7] * sc));
               }
+            }
+          }
+        }
+        if (p.amax) {
+          amax = warp_max(amax);
+          if (lane == 0) atomic_max_nonneg(p.amax + t.group * p.amax_stride, amax);
+        }
+      } else if (use_tma) {
+        // SwiGLU, full slab: gate and up pre-activations leave through TMA (one 64-column box each per two
+        // iterations), the e4m3 activation (a fifth of the bytes) through 8-byte stores.
+        const float sc = p.sc ? p.sc[t.group * p.sc_stride] : 1.f;
+        const int half_n = p.n / 2;
+        const int64_t out_row = t.row0 + row_in_tile;
+        uint8_t* adst = p.act_out + out_row * p.ld_act + t.nt * (kBlockN / 2);
+        const int col_base = t.nt * (kBlockN / 2);
+        float amax = 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockN / 2; c0 += 32) {
+          const int half = (c0 >> 5) & 1;
+          if (half == 0) {
+            if (lane == 0) bulk_wait_read<0>();  // both boxes are rewritten below
+            __syncwarp();
+          }
+          uint32_t rg[32], ru[32];
+          tmem_ld32(taddr + c0, rg);
+          tmem_ld32(taddr + kBlockN / 2 + c0, ru);
+          tc_wait_ld();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float hg[8], hu[8], a[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              hg[j] = __uint_as_float(rg[v * 8 + j]) * alpha;
+              hu[j] = __uint_as_float(ru[v * 8 + j]) * alpha;
+              a[j] = hg[j] / (1.f + __expf(-hg[j])) * hu[j];
+              amax = fmaxf(amax, fabsf(a[j]));
+            }
+            st_shared16(stage0 + staged_chunk(lane, half * 4 + v),
+                        make_uint4(pack_bf16x2(hg[0], hg[1]), pack_bf16x2(hg[2], hg[3]), pack_bf16x2(hg[4], hg[5]), pack_bf16x2(hg[6], hg[7])));
+            st_shared16(stage0 + 4096u + staged_chunk(lane, half * 4 + v),
+                        make_uint4(pack_bf16x2(hu[0], hu[1]), pack_bf16x2(hu[2], hu[3]), pack_bf16x2(hu[4], hu[5]), pack_bf16x2(hu[6], hu[7])));
+            *reinterpret_cast<uint2*>(adst + c0 + v * 8) =
+                make_uint2(cvt_fp8x4<FP8GMM_E4M3>(a[0] * sc, a[1] * sc, a[2] * sc, a[3] * sc),
+                           cvt_fp8x4<FP8GMM_E4M3>(a[4] * sc, a[5] * sc, a[6] * sc, a[7] * sc));
+          }
+          if (half == 1) {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&p.map_c, stage0, col_base + c0 - 32, row_coord);
+              tma_store_2d(&p.map_c, stage0 + 4096u, half_n + col_base + c0 - 32, row_coord);
+              bulk_commit();
             }
           }
         }
@@ -633,6 +749,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) bulk_wait_all();  // TMA stores of this warp have been written out
     if (p.profile && warp == 2 && lane == 0) {
       p.profile[blockIdx.x * 8 + 4] = wait_tfull;
       p.profile[blockIdx.x * 8 + 5] = busy;
@@ -697,6 +814,36 @@ int encode_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols)
     return FP8GMM_CUDA_ERROR;
   }
   return FP8GMM_OK;
+}
+
+// 2-D bf16 tensor (rows x cols, row pitch = cols) for the epilogue's TMA stores: box 32 rows x 64 columns
+// (128 bytes per row), SWIZZLE_128B to match the staging layout.
+int encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+  auto fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return FP8GMM_CUDA_ERROR;
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (store map) failed with %d (base %p, rows %llu, cols %llu)", static_cast<int>(r), base,
+              static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols));
+    return FP8GMM_CUDA_ERROR;
+  }
+  return FP8GMM_OK;
+}
+
+// FP8GMM_GEMM_EPILOGUE=direct switches the TMA-store epilogue off (every row is then written with per-thread
+// 16-byte stores); for experiments.
+bool tma_epilogue_enabled() {
+  const char* e = getenv("FP8GMM_GEMM_EPILOGUE");
+  return !(e != nullptr && e[0] == 'd');
 }
 
 uint32_t make_idesc(int a_format, int b_format, int ctas) {
@@ -839,6 +986,11 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  if (a->c_row_map == nullptr && a->activation != FP8GMM_ACT_GELU && tma_epilogue_enabled()) {
+    rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
+    if (rc != FP8GMM_OK) return rc;
+    p.tma_store = 1;
+  }
   return launch(p, ctas, static_cast<cudaStream_t>(stream));
 }
 
@@ -924,6 +1076,11 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  if (tma_epilogue_enabled()) {
+    const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
+    if (rc_map != FP8GMM_OK) return rc_map;
+    p.tma_store = 1;
+  }
   return launch(p, ctas, s);
 }
 
@@ -1047,5 +1204,10 @@ extern "C" int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* a, void* str
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  if (tma_epilogue_enabled()) {
+    const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
+    if (rc_map != FP8GMM_OK) return rc_map;
+    p.tma_store = 1;
+  }
   return launch(p, ctas, s);
 }

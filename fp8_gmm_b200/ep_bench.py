@@ -85,17 +85,28 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
         gi_host.copy_(x_dev.grad, non_blocking=True)
 
     warmup = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
     for _ in range(warmup):
         step()
     backend.device_status()
 
+    channel = None
+    if world > 1 and args.ep_transport == "peer":
+        from fp8_gmm_b200 import ep_peer
+
+        channel = ep_peer.EpContext.get(dev, model.group).channel
+        channel.wait_events = []
     timings = []
     backend.set_gemm_timings(timings)
     launches0 = backend.launch_count()
-    with ClockSampler(local_rank) as clocks:
+    with sampler as clocks:
         secs = _timed(step, args.steps, world)
     launches = backend.launch_count() - launches0
     backend.set_gemm_timings(None)
+    exposed_ms = None
+    if channel is not None:
+        exposed_ms = sum(s.elapsed_time(e) for s, e in channel.wait_events) / args.steps
+        channel.wait_events = None
     gemm_ms = sum(s.elapsed_time(e) for s, e, _ in timings)
     gemm_flops_local = sum(f for _, _, f in timings)
 
@@ -161,7 +172,8 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
         }
         if local_secs is not None:
             line["ep"] = {"local_ms_per_step_without_exchange": local_secs / args.steps * 1e3,
-                          "efficiency_vs_local": local_secs / secs}
+                          "efficiency_vs_local": local_secs / secs,
+                          "ms_per_step_waiting_for_rows_rank0": exposed_ms}
         if world == 1 and not args.no_cpu_baseline:
             cstep, cflops, desc = cpu_sample_step(H, F, ROWS_PER_EXPERT * 8)
             ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)

@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from . import backend
+from .grouped_linear import cast_weight_cached
 from .peer import PeerBuffer, PeerChannel
 from .recipe import get_fp8_te_dtype
 from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_sizes, to_torch_dtype
@@ -52,6 +53,7 @@ class PeerPlan:
         within = torch.cumsum(by_owner, 2) - by_owner                                   # exclusive over src
         self.blk_off = self.exp_off[:, :El, None] + within                              # (owner, j, src)
         self.by_owner = by_owner
+        self._counts_l, self._send_off_l, self._blk_off_l = counts.tolist(), self.send_off.tolist(), self.blk_off.tolist()
         self.local_sizes = rows_local[rank].tolist()
         self.rows_local_max = int(rows_local.sum(1).max())
         self.rows_own = int(counts[rank].sum())
@@ -72,11 +74,12 @@ class PeerPlan:
             j0, j1 = chunk
             El, r = self.experts_local, self.rank
             out = []
+            cnt, send, blk = self._counts_l[r], self._send_off_l[r], self._blk_off_l
             for o in self._peer_order():
                 for j in range(j0, j1):
-                    n = int(self.counts[r, o * El + j])
+                    n = cnt[o * El + j]
                     if n:
-                        out.append((o, int(self.blk_off[o, j, r]), int(self.send_off[r, o * El + j]), n))
+                        out.append((o, blk[o][j][r], send[o * El + j], n))
             self._lists[key] = out
         return self._lists[key]
 
@@ -87,11 +90,12 @@ class PeerPlan:
             j0, j1 = chunk
             El, r = self.experts_local, self.rank
             out = []
+            cnt, send, blk = self._counts_l, self._send_off_l, self._blk_off_l[r]
             for s in self._peer_order():
                 for j in range(j0, j1):
-                    n = int(self.counts[s, r * El + j])
+                    n = cnt[s][r * El + j]
                     if n:
-                        out.append((s, int(self.send_off[s, r * El + j]), int(self.blk_off[r, j, s]), n))
+                        out.append((s, send[s][r * El + j], blk[j][s], n))
             self._lists[key] = out
         return self._lists[key]
 
@@ -197,15 +201,6 @@ class EpContext:
         return buf.tensor((rows, cols), torch.bfloat16, on_release=back)
 
 
-def _cast_weight(weight, fp8_dtype, with_transpose, scale, amax):
-    g, n, k = weight.shape
-    w_fp8 = torch.empty(weight.shape, dtype=fp8_dtype, device=weight.device)
-    w_t = torch.empty(g, k, n, dtype=fp8_dtype, device=weight.device) if with_transpose else None
-    offs = [i * n for i in range(g + 1)]
-    backend.grouped_cast_transpose(weight.view(g * n, k), offs, w_fp8, w_t, offs, scale, amax)
-    return w_fp8, w_t
-
-
 def _rel(offsets, j0, j1):
     base = offsets[j0]
     return [o - base for o in offsets[j0:j1 + 1]]
@@ -248,9 +243,11 @@ class _PeerEpMlp(torch.autograd.Function):
         seq[0] = dispatch(chunks[0])
         # the weight casts run while the first rows are on their way
         ms = metas.get_meta_strided
-        fc1_w_fp8, fc1_w_t = _cast_weight(fc1_weight, fdt, need_dgrad, ms(_T.kWeightGroup1, _M.kScale), ms(_T.kWeightGroup1, _M.kAmax))
-        fc2_w_fp8, fc2_w_t = _cast_weight(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
-                                          ms(_T.kWeightGroup2, _M.kAmax))
+        cache, reuse = st["weight_cache"], st["reuse_weights"]
+        fc1_w_fp8, fc1_w_t = cast_weight_cached(fc1_weight, fdt, need_dgrad, ms(_T.kWeightGroup1, _M.kScale),
+                                                ms(_T.kWeightGroup1, _M.kAmax), cache, "fc1", reuse)
+        fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
+                                                ms(_T.kWeightGroup2, _M.kAmax), cache, "fc2", reuse)
         recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
         input_fp8 = torch.empty(rows, hidden, dtype=fdt, device=dev)
         input_t_fp8 = torch.empty(offs[-1], hidden, dtype=fdt, device=dev) if need_wgrad else None
@@ -391,7 +388,10 @@ def forward(module, input, group_sizes, is_first_microbatch, num_chunks):
     grad_on = torch.is_grad_enabled()
     want_gi = grad_on and input.requires_grad
     plan = ectx.plan(group_sizes, input.shape[1] * 2, num_chunks, want_gi)
-    st = {"mlp": mlp, "plan": plan, "ctx": ectx, "grad_enabled": grad_on}
+    mlp.get_fp8_weights_scratchpad(is_first_microbatch)
+    st = {"mlp": mlp, "plan": plan, "ctx": ectx, "grad_enabled": grad_on,
+          "weight_cache": None if is_first_microbatch is None else mlp._fp8_weights,
+          "reuse_weights": is_first_microbatch is False}
     with mlp.prepare_forward(input, is_first_microbatch, mlp.num_groups * 2):
         if grad_on:
             return _PeerEpMlp.apply(input, mlp.fc1_weight, mlp.fc2_weight, st)

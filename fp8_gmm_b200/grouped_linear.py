@@ -8,6 +8,8 @@ saved-tensor layout, meta slots), re-implemented on this package's kernels:
 * the forward / dgrad GEMM is one launch with the de-scale fused (the reference's CUTLASS path needs a
   second pass, fp8_gmm/backend.py:78-82);
 * the weight gradient is one grouped launch (the reference loops over groups, :165-182);
+* ``is_first_microbatch`` works (the reference forces None): True casts the weights and keeps the FP8 copies, False
+  reuses them and leaves the scales alone, so gradient accumulation pays the weight cast once per optimizer step;
 * groups with zero rows are accepted (the reference asserts, :205): they produce no output rows and a
   zero weight gradient.
 """
@@ -24,7 +26,7 @@ _T, _M = Fp8TensorType, MetaTensorType
 
 class _GroupedLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, weight, group_sizes, fp8_meta, is_grad_enabled, cutlass):
+    def forward(ctx, input, weight, group_sizes, fp8_meta, is_grad_enabled, cutlass, weight_cache=None, reuse_weights=False):
         need_wgrad = is_grad_enabled and weight.requires_grad
         need_dgrad = is_grad_enabled and input.requires_grad
         num_groups, padded, cumsums, padded_cumsums = cumsum_group_sizes(group_sizes.tolist(), need_padding=need_wgrad)
@@ -41,12 +43,9 @@ class _GroupedLinear(torch.autograd.Function):
         backend.grouped_cast_transpose(
             input, cumsums, input_fp8, input_t_fp8, offs,
             metas.get_meta_strided(_T.kInputGroup1, _M.kScale), metas.get_meta_strided(_T.kInputGroup1, _M.kAmax))
-        weight_fp8 = torch.empty(weight.shape, dtype=torch_dtype, device=weight.device)
-        weight_t_fp8 = torch.empty(num_groups, k, n, dtype=torch_dtype, device=weight.device) if need_dgrad else None
-        w_offs = [g * n for g in range(num_groups + 1)]
-        backend.grouped_cast_transpose(
-            weight.view(num_groups * n, k), w_offs, weight_fp8, weight_t_fp8, w_offs,
-            metas.get_meta_strided(_T.kWeightGroup1, _M.kScale), metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax))
+        weight_fp8, weight_t_fp8 = cast_weight_cached(
+            weight, torch_dtype, need_dgrad, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
+            metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax), weight_cache, "weight", reuse_weights)
         out = backend.fp8_gmm(
             input_fp8, weight_fp8, group_sizes,
             metas.get_meta_strided(_T.kInputGroup1, _M.kScaleInv), metas.get_meta_strided(_T.kWeightGroup1, _M.kScaleInv),
@@ -91,7 +90,29 @@ class _GroupedLinear(torch.autograd.Function):
                 grad_out_t_fp8, input_t_fp8, offs, n, k,
                 metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScaleInv),
                 metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
-        return grad_input, grad_weight, None, None, None, None
+        return grad_input, grad_weight, None, None, None, None, None, None
+
+
+def cast_weight_cached(weight, fp8_dtype, with_transpose, scale, amax, cache, key, reuse):
+    """(G, N, K) bf16 weights -> FP8 copy and, with ``with_transpose``, the per-expert transposes (G, K, N).
+
+    ``cache`` (a dict owned by the module, or None) keeps the FP8 weights between micro-batches: with ``reuse`` the
+    cast is skipped when the cached copy fits (same dtype, a transpose present if one is needed).  This is the
+    ``is_first_microbatch`` protocol of Transformer Engine modules, which the reference switches off
+    (reference fp8_gmm/grouped_linear.py:200-202): weights only change at the optimizer step, so their cast and
+    transpose need not be repeated for every micro-batch of a gradient-accumulation step."""
+    if cache is not None and reuse and key in cache:
+        w_fp8, w_t = cache[key]
+        if w_fp8.dtype == fp8_dtype and w_fp8.shape == weight.shape and (w_t is not None or not with_transpose):
+            return w_fp8, (w_t if with_transpose else None)
+    g, n, k = weight.shape
+    w_fp8 = torch.empty(weight.shape, dtype=fp8_dtype, device=weight.device)
+    w_t = torch.empty(g, k, n, dtype=fp8_dtype, device=weight.device) if with_transpose else None
+    offs = [i * n for i in range(g + 1)]
+    backend.grouped_cast_transpose(weight.view(g * n, k), offs, w_fp8, w_t, offs, scale, amax)
+    if cache is not None:
+        cache[key] = (w_fp8, w_t)
+    return w_fp8, w_t
 
 
 class GroupedLinear(Fp8GmmBaseModule):
@@ -112,10 +133,14 @@ class GroupedLinear(Fp8GmmBaseModule):
         bound = math.sqrt(1.0 / in_features)
         torch.nn.init.uniform_(self.weight_tensor.data, -bound, bound)
         self.cutlass = cutlass
+        self._fp8_weights = {}
 
     def get_fp8_weights_scratchpad(self, is_first_microbatch):
-        assert is_first_microbatch is None
-        return [None, None]
+        """[weight_fp8, weight_t_fp8] kept from the first micro-batch, or [None, None] without caching
+        (``is_first_microbatch is None``, the only mode of the reference, fp8_gmm/grouped_linear.py:200-202)."""
+        if is_first_microbatch is None:
+            self._fp8_weights.clear()
+        return list(self._fp8_weights.get("weight", (None, None)))
 
     def forward(self, input, group_sizes, is_first_microbatch=None):
         if not torch.is_tensor(group_sizes):
@@ -125,5 +150,7 @@ class GroupedLinear(Fp8GmmBaseModule):
                 fn, args = _GroupedLinear.apply, []
             else:
                 fn, args = _GroupedLinear.forward, [None]
-            args += [input, self.weight_tensor, group_sizes, self.fp8_meta, torch.is_grad_enabled(), self.cutlass]
+            self.get_fp8_weights_scratchpad(is_first_microbatch)
+            args += [input, self.weight_tensor, group_sizes, self.fp8_meta, torch.is_grad_enabled(), self.cutlass,
+                     None if is_first_microbatch is None else self._fp8_weights, is_first_microbatch is False]
             return fn(*args)

@@ -13,25 +13,17 @@ import math
 import torch
 
 from . import backend
+from .grouped_linear import cast_weight_cached
 from .recipe import Fp8GmmBaseModule, get_fp8_te_dtype
 from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_sizes, to_torch_dtype
 
 _T, _M = Fp8TensorType, MetaTensorType
 
 
-def _cast_weight(weight, fp8_dtype, with_transpose, scale, amax):
-    g, n, k = weight.shape
-    w_fp8 = torch.empty(weight.shape, dtype=fp8_dtype, device=weight.device)
-    w_t = torch.empty(g, k, n, dtype=fp8_dtype, device=weight.device) if with_transpose else None
-    offs = [i * n for i in range(g + 1)]
-    backend.grouped_cast_transpose(weight.view(g * n, k), offs, w_fp8, w_t, offs, scale, amax)
-    return w_fp8, w_t
-
-
 class _GroupedMlp(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, fc1_weight, fc2_weight, group_sizes, fp8_meta, is_grad_enabled, has_tp, tp_group, activation,
-                perm=None):
+                perm=None, weight_cache=None, reuse_weights=False):
         input_requires_grad = input.requires_grad
         weight_requires_grad = fc1_weight.requires_grad
         need_wgrad = is_grad_enabled and weight_requires_grad
@@ -57,13 +49,15 @@ class _GroupedMlp(torch.autograd.Function):
             backend.blocked_cast(input, input_fp8, perm, x_scale, x_amax, num_groups)
             if need_wgrad:
                 backend.grouped_cast_transpose(input_fp8, cumsums, None, input_t_fp8, offs, None, None)
-        fc1_w_fp8, fc1_w_t = _cast_weight(
+        fc1_w_fp8, fc1_w_t = cast_weight_cached(
             fc1_weight, torch_dtype, need_dgrad,
-            metas.get_meta_strided(_T.kWeightGroup1, _M.kScale), metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax))
+            metas.get_meta_strided(_T.kWeightGroup1, _M.kScale), metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax),
+            weight_cache, "fc1", reuse_weights)
         # d(activation) feeds the fc1 weight gradient too, so fc2's transpose is needed whenever anything trains
-        fc2_w_fp8, fc2_w_t = _cast_weight(
+        fc2_w_fp8, fc2_w_t = cast_weight_cached(
             fc2_weight, torch_dtype, need_dgrad or need_wgrad,
-            metas.get_meta_strided(_T.kWeightGroup2, _M.kScale), metas.get_meta_strided(_T.kWeightGroup2, _M.kAmax))
+            metas.get_meta_strided(_T.kWeightGroup2, _M.kScale), metas.get_meta_strided(_T.kWeightGroup2, _M.kAmax),
+            weight_cache, "fc2", reuse_weights)
 
         pre_act = torch.empty(input.shape[0], fc1_out, dtype=torch.bfloat16, device=input.device)
         act_fp8 = torch.empty(input.shape[0], ffn, dtype=torch_dtype, device=input.device)
@@ -153,7 +147,7 @@ class _GroupedMlp(torch.autograd.Function):
                 metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
         if handle is not None:
             handle.wait()
-        return grad_input, grad_fc1_weight, grad_fc2_weight, None, None, None, None, None, None, None
+        return grad_input, grad_fc1_weight, grad_fc2_weight, None, None, None, None, None, None, None, None, None
 
 
 class GroupedMlp(Fp8GmmBaseModule):
@@ -173,10 +167,14 @@ class GroupedMlp(Fp8GmmBaseModule):
         b1, b2 = math.sqrt(1.0 / in_features), math.sqrt(1.0 / out_features)
         torch.nn.init.uniform_(self.fc1_weight.data, -b1, b1)
         torch.nn.init.uniform_(self.fc2_weight.data, -b2, b2)
+        self._fp8_weights = {}
 
     def get_fp8_weights_scratchpad(self, is_first_microbatch):
-        assert is_first_microbatch is None
-        return [None, None, None, None]
+        """[fc1_fp8, fc1_t_fp8, fc2_fp8, fc2_t_fp8] kept from the first micro-batch, or Nones without caching
+        (``is_first_microbatch is None``, the only mode of the reference, fp8_gmm/grouped_mlp.py:343-345)."""
+        if is_first_microbatch is None:
+            self._fp8_weights.clear()
+        return list(self._fp8_weights.get("fc1", (None, None))) + list(self._fp8_weights.get("fc2", (None, None)))
 
     def forward(self, input, group_sizes, has_tp=False, tp_group=None, is_first_microbatch=None, row_permutation=None):
         """``row_permutation`` (a backend.RowPermutation, optional, not in the reference): rows of ``input`` and of
@@ -189,8 +187,10 @@ class GroupedMlp(Fp8GmmBaseModule):
                 fn, args = _GroupedMlp.apply, []
             else:
                 fn, args = _GroupedMlp.forward, [None]
+            self.get_fp8_weights_scratchpad(is_first_microbatch)
             args += [input, self.fc1_weight, self.fc2_weight, group_sizes, self.fp8_meta, torch.is_grad_enabled(),
-                     has_tp, tp_group, self.activation, row_permutation]
+                     has_tp, tp_group, self.activation, row_permutation,
+                     None if is_first_microbatch is None else self._fp8_weights, is_first_microbatch is False]
             return fn(*args)
 
 

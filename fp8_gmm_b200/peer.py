@@ -107,6 +107,7 @@ class PeerChannel:
         # 575-600 GB/s per direction either way, so one stream is the default)
         self.side = [torch.cuda.Stream(device=device) for _ in range(max(copy_streams, 1) - 1)]
         self.seq = 0
+        self.wait_events = None   # a list here collects (start, end) CUDA events around every wait (benchmarks)
         arr = (ctypes.c_void_p * self.world)()
         for r in range(self.world):
             arr[r] = self.flags.ptrs[r] + 4 * self.rank       # my word in rank r's page
@@ -142,8 +143,16 @@ class PeerChannel:
 
     def wait(self, seq):
         """Compute stream waits for round ``seq`` of every sender (bounded on the device; see fp8gmm_peer_wait)."""
+        trace = self.wait_events
+        if trace is not None:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
         check(lib.fp8gmm_peer_wait(self.flags.local, self.world, seq, torch.cuda.current_stream(self.device).cuda_stream),
               "peer_wait")
+        if trace is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            trace.append((start, end))
 
     def close(self):
         self.flags.close()

@@ -250,3 +250,41 @@ def test_row_permutation_is_equivalent_to_gather_scatter(cuda, act):
     assert torch.equal(y_p[to_em], y_e) and torch.equal(gx_p[to_em], gx_e)
     assert torch.equal(gw1_p, gw1_e) and torch.equal(gw2_p, gw2_e)
     assert torch.equal(af_p, af_e) and torch.equal(ab_p, ab_e)
+
+
+@pytest.mark.parametrize("kind", ["linear", "mlp"])
+def test_weight_cache_across_microbatches(cuda, kind):
+    """is_first_microbatch=True casts and keeps the FP8 weights, False reuses them: two micro-batches give the same
+    results as with is_first_microbatch=None as long as the scales do not move in between (update interval 1000),
+    the cached tensors are the very same objects, and the number of kernel launches drops by the weight casts."""
+    import fp8_gmm_b200 as fg
+
+    sizes, k, n = [40, 0, 24], 64, 128
+    make = (lambda: fg.GroupedLinear(k, n, 3, torch.bfloat16, device=cuda)) if kind == "linear" else (
+        lambda: fg.GroupedMlp(k, n, 3, torch.bfloat16, device=cuda, activation="swiglu"))
+    torch.manual_seed(0)
+    ref_layer = make()
+    layer = make()
+    layer.load_state_dict(copy.deepcopy(ref_layer.state_dict()))
+    xs = [randn_bf16((64, k), 20 + i).to(cuda) for i in range(2)]
+    results = {}
+    for name, mod, flags in (("plain", ref_layer, [None, None]), ("cached", layer, [True, False])):
+        outs, launches = [], []
+        for x, flag in zip(xs, flags):
+            xin = x.clone().requires_grad_(True)
+            before = fg.backend.launch_count()
+            with fg.fp8_autocast(enabled=True, fp8_recipe=fg.DelayedScaling(interval=1000, amax_history_len=4)):
+                y = mod(xin, torch.tensor(sizes), is_first_microbatch=flag)
+            launches.append(fg.backend.launch_count() - before)
+            y.float().sum().backward()
+            outs.append((y.detach().clone(), xin.grad.clone()))
+        results[name] = (outs, launches, [p.grad.clone() for p in mod.parameters()])
+    for (y0, g0), (y1, g1) in zip(results["plain"][0], results["cached"][0]):
+        assert torch.equal(y0, y1) and torch.equal(g0, g1)
+    for w0, w1 in zip(results["plain"][2], results["cached"][2]):
+        assert torch.equal(w0, w1)
+    n_weights = 1 if kind == "linear" else 2
+    assert results["cached"][1][1] == results["plain"][1][1] - n_weights, results
+    pad = layer.get_fp8_weights_scratchpad(False)
+    assert all(t is not None and t.dtype == torch.float8_e4m3fn for t in pad)
+    fg.backend.device_status()
