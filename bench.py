@@ -56,7 +56,8 @@ def parse():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                    help="expert-parallel leg: copy-engine pushes into peer memory pipelined with the GEMMs, or NCCL all-to-all")
-    p.add_argument("--ep-chunks", type=int, default=4, help="expert chunks of the peer-transport pipeline")
+    p.add_argument("--ep-chunks", default="4", help="expert chunks of the peer-transport pipeline: a count, 'tapered', "
+                   "or comma-separated expert counts per chunk")
     return p.parse_args()
 
 

@@ -41,7 +41,14 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;  // bytes == fp8 elements
-constexpr int kSuperRows = 32;  // m-tiles per super-row of the tile order
+// Tile order inside a group: super-rows of this many rows, m fastest inside a super-row.  With a short
+// contraction a 4096-row band of A stays in L2 while the n-tiles sweep past it, so A and B are each read from
+// DRAM about once (measured: 1.10 GB for 1.07 GB of operands, N = 28672, K = 4096).  With a long contraction
+// neither band fits, reuse only happens among the ~74 tiles in flight, and a squarer wave (8 x 9 tiles rather
+// than 16 x 4.6) touches fewer distinct operand rows.
+constexpr int kSuperRowsShortK = 4096;
+constexpr int kSuperRowsLongK = 2048;
+constexpr int kLongK = 8192;
 constexpr int kThreads = 192;
 constexpr int kTileABytes = kBlockM * kBlockK;          // 16 KiB
 constexpr int kTileBBytes = kBlockN * kBlockK;          // 32 KiB
@@ -69,6 +76,7 @@ struct GemmParams {
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
   int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
+  int super_tiles;     // m-tiles per super-row of the tile order (see decode_tile)
   int tma_store;       // 1: full 32-row slabs of a tile leave through shared memory + TMA stores (map_c is valid)
   int mode;
   int activation;
@@ -242,7 +250,7 @@ struct TileInfo {
 template <int kCtas>
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile, int rank) {
   constexpr int kTileM = kBlockM * kCtas;
-  constexpr int kSuper = kSuperRows / kCtas;
+  const int kSuper = p.super_tiles;
   TileInfo t;
   const int g = upper_slot(p.tile_start, p.num_groups, tile);
   const int local = tile - p.tile_start[g];
@@ -986,6 +994,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  p.super_tiles = (a->k > kLongK ? kSuperRowsLongK : kSuperRowsShortK) / tile_m;
   if (a->c_row_map == nullptr && a->activation != FP8GMM_ACT_GELU && tma_epilogue_enabled()) {
     rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
     if (rc != FP8GMM_OK) return rc;
@@ -1076,6 +1085,7 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
   if (tma_epilogue_enabled()) {
     const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
     if (rc_map != FP8GMM_OK) return rc_map;
@@ -1204,6 +1214,7 @@ extern "C" int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* a, void* str
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
   if (tma_epilogue_enabled()) {
     const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
     if (rc_map != FP8GMM_OK) return rc_map;

@@ -274,6 +274,194 @@ __global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspo
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Activation-backward variants (kDgelu, kDswiglu): two or three input streams per output.
+// Holding 16 rows of every stream plus the packed transposed bytes in registers (as the cast kernel does for
+// its single stream) leaves room for one CTA per SM only and too few loads in flight.  Here a thread walks
+// its 16 rows in four batches of four: the loads of a batch (4 rows x 2-3 streams x 16 bytes) are issued
+// together, the transposed bytes of a batch are one 32-bit word per column and go to shared memory at once.
+// About 100 registers, two CTAs per SM.  Shared-memory layout per half: [column][128 row bytes]; inside a
+// column the eight 16-byte chunks are XOR-swizzled with the writer's lane & 7 (as in the cast kernel) and the
+// four words of a chunk with lane >> 3, which makes the 32-bit stores of a warp hit 32 different banks.
+// ---------------------------------------------------------------------------------------------
+template <int kMode, int kFormat>
+__global__ void __launch_bounds__(kThreads, 2) act_pad_kernel(const __grid_constant__ PadArgs args) {
+  static_assert(kWarps == 8, "the word swizzle below assumes 8 warps (128-row tiles)");
+  constexpr int kHalves = (kMode == kDswiglu) ? 2 : 1;
+  constexpr int kHalfBytes = kTileCols * kTileRows;
+  extern __shared__ __align__(16) uint8_t smem_t[];
+  __shared__ float staging[kThreads / 32];
+
+  const int tile = blockIdx.x;
+  const int t = upper_slot(args.tile_start, args.num, tile);
+  const PadDesc& d = args.d[t];
+  const int local = tile - args.tile_start[t];
+  const int tile_row = (local / d.tiles_n) * kTileRows;
+  const int tile_col = (local % d.tiles_n) * kTileCols;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rows = d.rows, cols = d.cols;
+  const int64_t ld_in = cols;
+  const int64_t ld_io = (kMode == kDswiglu) ? 2 * (int64_t)cols : cols;
+  const float scale = d.scale ? *d.scale : 1.0f;
+  const int col0 = tile_col + lane * 8;
+  const int row0 = tile_row + warp * 16;
+  const bool fast_io = d.fast_io != 0;
+  const uint16_t* in = static_cast<const uint16_t*>(d.in);
+  const uint16_t* in2 = static_cast<const uint16_t*>(d.in2);
+  float amax = 0.f;
+
+#pragma unroll 1
+  for (int b = 0; b < 4; ++b) {
+    uint4 px[4], pg[4], pu[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = row0 + 4 * b + r;
+      px[r] = pg[r] = pu[r] = make_uint4(0, 0, 0, 0);
+      if (fast_io && row < rows && col0 < cols) {
+        px[r] = ld_stream16(in + (int64_t)row * ld_in + col0);
+        pg[r] = ld_stream16(in2 + (int64_t)row * ld_io + col0);
+        if (kMode == kDswiglu) pu[r] = ld_stream16(in2 + (int64_t)row * ld_io + cols + col0);
+      }
+    }
+    uint32_t tw[kHalves][8];
+#pragma unroll
+    for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tw[h][j] = 0;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = row0 + 4 * b + r;
+      const bool live = row < rows && col0 < cols;
+      float x[8], y[8], z[8];
+      if (fast_io) {
+        const uint32_t xw[4] = {px[r].x, px[r].y, px[r].z, px[r].w};
+        const uint32_t gw[4] = {pg[r].x, pg[r].y, pg[r].z, pg[r].w};
+        const uint32_t uw[4] = {pu[r].x, pu[r].y, pu[r].z, pu[r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          x[2 * j] = bf16_lo(xw[j]), x[2 * j + 1] = bf16_hi(xw[j]);
+          y[2 * j] = bf16_lo(gw[j]), y[2 * j + 1] = bf16_hi(gw[j]);
+          z[2 * j] = bf16_lo(uw[j]), z[2 * j + 1] = bf16_hi(uw[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          x[j] = y[j] = z[j] = 0.f;
+          if (live && col0 + j < cols) {
+            x[j] = __uint_as_float((uint32_t)in[(int64_t)row * ld_in + col0 + j] << 16);
+            y[j] = __uint_as_float((uint32_t)in2[(int64_t)row * ld_io + col0 + j] << 16);
+            if (kMode == kDswiglu) z[j] = __uint_as_float((uint32_t)in2[(int64_t)row * ld_io + cols + col0 + j] << 16);
+          }
+        }
+      }
+      float v0[8], v1[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (kMode == kDgelu) {
+          v0[j] = x[j] * dgelu_tanh(y[j]);
+          v1[j] = 0.f;
+        } else {  // d gate = dy * up * d silu(gate), d up = dy * silu(gate)
+          const float sg = 1.f / (1.f + __expf(-y[j]));
+          v0[j] = x[j] * z[j] * (sg * (1.f + y[j] * (1.f - sg)));
+          v1[j] = x[j] * (y[j] * sg);
+        }
+        amax = fmaxf(fabsf(v0[j]), amax);
+        if (kMode == kDswiglu) amax = fmaxf(fabsf(v1[j]), amax);
+      }
+#pragma unroll
+      for (int h = 0; h < kHalves; ++h) {
+        const float* v = h == 0 ? v0 : v1;
+        const uint32_t q01 = cvt_fp8x2<kFormat>(scale * v[0], scale * v[1]);
+        const uint32_t q23 = cvt_fp8x2<kFormat>(scale * v[2], scale * v[3]);
+        const uint32_t q45 = cvt_fp8x2<kFormat>(scale * v[4], scale * v[5]);
+        const uint32_t q67 = cvt_fp8x2<kFormat>(scale * v[6], scale * v[7]);
+        const uint32_t lo = q01 | (q23 << 16), hi = q45 | (q67 << 16);
+        if (d.out != nullptr && live) {
+          uint8_t* p = d.out + (int64_t)row * ld_io + (int64_t)h * cols + col0;
+          if (fast_io) {
+            st_stream8(p, make_uint2(lo, hi));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col0 + j < cols) p[j] = (uint8_t)(((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xFFu);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t byte = ((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xFFu;
+          tw[h][j] |= byte << (8 * r);
+        }
+      }
+    }
+    if (d.out_t != nullptr) {
+#pragma unroll
+      for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = lane * 8 + j;
+          *reinterpret_cast<uint32_t*>(smem_t + h * kHalfBytes + c * kTileRows + ((warp ^ (lane & 7)) << 4) +
+                                       ((b ^ (lane >> 3)) << 2)) = tw[h][j];
+        }
+    }
+  }
+
+  if (d.out_t != nullptr) {
+    __syncthreads();
+    const int padded_rows = d.padded_rows;
+#pragma unroll
+    for (int h = 0; h < kHalves; ++h) {
+      uint8_t* out_t = d.out_t + (int64_t)h * cols * padded_rows;
+      const uint8_t* half = smem_t + h * kHalfBytes;
+      if (d.fast_t) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int idx = it * kThreads + tid;
+          const int c = idx >> 3, chunk = idx & 7;
+          const int col = tile_col + c, row = tile_row + chunk * 16;
+          if (col < cols && row < padded_rows) {
+            const uint4 v = *reinterpret_cast<const uint4*>(half + c * kTileRows + ((chunk ^ ((c >> 3) & 7)) << 4));
+            // the writer of column c was lane c >> 3, so its words sit at position (batch ^ (c >> 6)); c >> 6 == it >> 1
+            uint4 o = v;
+            if ((it >> 1) & 1) o = make_uint4(o.y, o.x, o.w, o.z);
+            if ((it >> 1) & 2) o = make_uint4(o.z, o.w, o.x, o.y);
+            st_stream16(out_t + (int64_t)col * padded_rows + row, o);
+          }
+        }
+      } else {
+        for (int idx = tid; idx < kTileCols * kTileRows; idx += kThreads) {
+          const int c = idx / kTileRows, r = idx % kTileRows;
+          const int col = tile_col + c, row = tile_row + r;
+          if (col < cols && row < padded_rows)
+            out_t[(int64_t)col * padded_rows + row] =
+                half[c * kTileRows + (((r >> 4) ^ ((c >> 3) & 7)) << 4) + ((((r >> 2) & 3) ^ (c >> 6)) << 2) + (r & 3)];
+        }
+      }
+    }
+  }
+
+  if (d.amax != nullptr) {
+    amax = warp_max(amax);
+    if (lane == 0) staging[warp] = amax;
+    __syncthreads();
+    if (tid < 32) {
+      float m = tid < kThreads / 32 ? staging[tid] : 0.f;
+      m = warp_max(m);
+      if (tid == 0) atomic_max_nonneg(d.amax, m);
+    }
+  }
+}
+
+template <int kMode, int kFormat>
+int launch_act(const PadArgs& args, cudaStream_t s) {
+  constexpr int kSmem = kTileCols * kTileRows * (kMode == kDswiglu ? 2 : 1);
+  if (kSmem > 48 * 1024)
+    FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(act_pad_kernel<kMode, kFormat>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  act_pad_kernel<kMode, kFormat><<<args.tile_start[args.num], kThreads, kSmem, s>>>(args);
+  FP8GMM_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return FP8GMM_OK;
+}
+
 template <int kMode>
 int launch_mode(const PadArgs& args, int out_format, cudaStream_t s) {
   const int grid = args.tile_start[args.num];
@@ -297,8 +485,12 @@ int flush(PadArgs& args, int mode, int out_format, cudaStream_t s) {
   int rc = FP8GMM_OK;
   switch (mode) {
     case kCast: rc = launch_mode<kCast>(args, out_format, s); break;
-    case kDgelu: rc = launch_mode<kDgelu>(args, out_format, s); break;
-    case kDswiglu: rc = launch_mode<kDswiglu>(args, out_format, s); break;
+    case kDgelu:
+      rc = out_format == FP8GMM_E4M3 ? launch_act<kDgelu, FP8GMM_E4M3>(args, s) : launch_act<kDgelu, FP8GMM_E5M2>(args, s);
+      break;
+    case kDswiglu:
+      rc = out_format == FP8GMM_E4M3 ? launch_act<kDswiglu, FP8GMM_E4M3>(args, s) : launch_act<kDswiglu, FP8GMM_E5M2>(args, s);
+      break;
     default: rc = launch_mode<kTranspose>(args, out_format, s); break;
   }
   args.num = 0;

@@ -59,8 +59,10 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
     out_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
     gi_host = torch.empty(rows, H, dtype=torch.bfloat16).pin_memory()
     torch.manual_seed(3000 + rank)
+    spec = str(args.ep_chunks)
+    chunks = spec if spec == "tapered" else int(spec) if spec.isdigit() else [int(v) for v in spec.split(",")]
     model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu",
-                                 transport=args.ep_transport, num_chunks=args.ep_chunks)
+                                 transport=args.ep_transport, num_chunks=chunks)
     with torch.no_grad():
         model.mlp.fc1_weight.normal_(0.0, 0.02)
         model.mlp.fc2_weight.normal_(0.0, 0.02)
@@ -94,8 +96,9 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
     if world > 1 and args.ep_transport == "peer":
         from fp8_gmm_b200 import ep_peer
 
-        channel = ep_peer.EpContext.get(dev, model.group).channel
-        channel.wait_events = []
+        ectx = ep_peer.EpContext.get(dev, model.group)
+        channel = ectx.channel
+        channel.wait_events = ectx.channel_back.wait_events = []   # one shared list, in program order
     timings = []
     backend.set_gemm_timings(timings)
     launches0 = backend.launch_count()
@@ -106,7 +109,9 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
     exposed_ms = None
     if channel is not None:
         exposed_ms = sum(s.elapsed_time(e) for s, e in channel.wait_events) / args.steps
-        channel.wait_events = None
+        per_step = len(channel.wait_events) // args.steps
+        last_step_waits = [round(s.elapsed_time(e), 3) for s, e in channel.wait_events[-per_step:]]
+        channel.wait_events = ectx.channel_back.wait_events = None
     gemm_ms = sum(s.elapsed_time(e) for s, e, _ in timings)
     gemm_flops_local = sum(f for _, _, f in timings)
 
@@ -174,6 +179,8 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
             line["ep"] = {"local_ms_per_step_without_exchange": local_secs / args.steps * 1e3,
                           "efficiency_vs_local": local_secs / secs,
                           "ms_per_step_waiting_for_rows_rank0": exposed_ms}
+            if exposed_ms is not None:
+                line["ep"]["waits_ms_last_step_rank0"] = last_step_waits
         if world == 1 and not args.no_cpu_baseline:
             cstep, cflops, desc = cpu_sample_step(H, F, ROWS_PER_EXPERT * 8)
             ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)

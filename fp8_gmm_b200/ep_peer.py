@@ -30,6 +30,36 @@ from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_s
 _T, _M = Fp8TensorType, MetaTensorType
 
 
+_TAPER = (1, 2, 4, 4, 3, 2)  # sixteenths of the local experts per chunk: small first and last rounds, which nothing hides
+
+
+def chunk_bounds(experts_local, spec):
+    """[(first expert, end expert)] of the pipeline's chunks.  ``spec``: an int (that many even chunks), "tapered"
+    (chunks of 1/16, 1/8, 1/4, 1/4, 3/16, 1/8 of the experts: the first dispatch and the last combine round, which
+    no computation overlaps, stay short), or an explicit sequence of expert counts summing to ``experts_local``."""
+    El = experts_local
+    if isinstance(spec, str):
+        assert spec == "tapered", spec
+        sizes = [max(1, round(El * f / 16)) for f in _TAPER] if El >= 6 else [1] * El
+        while sum(sizes) > El:
+            sizes[sizes.index(max(sizes))] -= 1
+        while sum(sizes) < El:
+            sizes[sizes.index(max(sizes))] += 1
+    elif isinstance(spec, int):
+        C = max(1, min(spec, El))
+        bounds = [round(i * El / C) for i in range(C + 1)]
+        sizes = [bounds[i + 1] - bounds[i] for i in range(C)]
+    else:
+        sizes = [int(v) for v in spec]
+        assert sum(sizes) == El and min(sizes) >= 0, "chunk sizes must sum to the number of local experts"
+    out, start = [], 0
+    for n in sizes:
+        if n > 0:
+            out.append((start, start + n))
+        start += n
+    return out
+
+
 class PeerPlan:
     """Row bookkeeping of one exchange, derived from everybody's group sizes.
 
@@ -58,9 +88,7 @@ class PeerPlan:
         self.rows_local_max = int(rows_local.sum(1).max())
         self.rows_own = int(counts[rank].sum())
         self.rows_own_max = int(counts.sum(1).max())
-        C = max(1, min(num_chunks, El))
-        bounds = [round(i * El / C) for i in range(C + 1)]
-        self.chunks = [(bounds[i], bounds[i + 1]) for i in range(C) if bounds[i + 1] > bounds[i]]
+        self.chunks = chunk_bounds(El, num_chunks)
         self._lists = {}
 
     def _peer_order(self):
@@ -139,7 +167,9 @@ class EpContext:
     def __init__(self, device, group):
         self.device, self.group = device, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.channel = PeerChannel(device, group)
+        # two channels = two side streams: dispatch and combine copies run on different copy engines at the same time
+        self.channel = PeerChannel(device, group)          # dispatch rounds
+        self.channel_back = PeerChannel(device, group)     # combine rounds
         self.pool = _Pool(device, group)
         self.recv = None
 
@@ -212,7 +242,7 @@ class _PeerEpMlp(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, fc1_weight, fc2_weight, st):
         mlp, plan, ectx = st["mlp"], st["plan"], st["ctx"]
-        ch = ectx.channel
+        ch, ch_back = ectx.channel, ectx.channel_back
         fp8_meta, activation = mlp.fp8_meta, mlp.activation
         grad_on = st["grad_enabled"]
         need_wgrad = grad_on and fc1_weight.requires_grad
@@ -244,8 +274,7 @@ class _PeerEpMlp(torch.autograd.Function):
         # the weight casts run while the first rows are on their way
         ms = metas.get_meta_strided
         cache, reuse = st["weight_cache"], st["reuse_weights"]
-        fc1_w_fp8, fc1_w_t = cast_weight_cached(fc1_weight, fdt, need_dgrad, ms(_T.kWeightGroup1, _M.kScale),
-                                                ms(_T.kWeightGroup1, _M.kAmax), cache, "fc1", reuse)
+        fc1_w_fp8, fc1_w_t = st["fc1_fp8"]   # cast before the size exchange, so the GPU had work during the host sync
         fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
                                                 ms(_T.kWeightGroup2, _M.kAmax), cache, "fc2", reuse)
         recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
@@ -278,9 +307,9 @@ class _PeerEpMlp(torch.autograd.Function):
                     ms(_T.kInputGroup2, _M.kScaleInv, j0), ms(_T.kWeightGroup2, _M.kScaleInv, j0),
                     c=out_local[r0:r1], backward=False)
             o_ptr = out_local.data_ptr()
-            last = ch.push([(out_ptrs[s] + d * row_bytes, o_ptr + l * row_bytes, n * row_bytes)
-                            for s, d, l, n in plan.combine_blocks((j0, j1))])
-        ch.wait(last)
+            last = ch_back.push([(out_ptrs[s] + d * row_bytes, o_ptr + l * row_bytes, n * row_bytes)
+                                 for s, d, l, n in plan.combine_blocks((j0, j1))])
+        ch_back.wait(last)
         if grad_on:
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
             # backward never runs
@@ -298,7 +327,7 @@ class _PeerEpMlp(torch.autograd.Function):
         input_t_fp8, fc1_w_t, fc2_w_t, pre_act, act_fp8 = ctx.saved_tensors
         st, metas, cumsums, offs, sizes_cpu = ctx.st, ctx.metas, ctx.cumsums, ctx.offs, ctx.sizes_cpu
         mlp, plan, ectx = st["mlp"], st["plan"], st["ctx"]
-        ch = ectx.channel
+        ch, ch_back = ectx.channel, ectx.channel_back
         fp8_meta, activation = mlp.fp8_meta, mlp.activation
         fp8_meta["prepare_backward"]()
         gdt = to_torch_dtype(get_fp8_te_dtype(fp8_meta["recipe"], fprop_tensor=False))
@@ -370,14 +399,14 @@ class _PeerEpMlp(torch.autograd.Function):
                 grad_fc2[j0:j1].zero_()
             if dgrad:
                 g_ptr = gi_local.data_ptr()
-                last = ch.push([(gi_ptrs[s] + d * row_bytes, g_ptr + l * row_bytes, n * row_bytes)
-                                for s, d, l, n in plan.combine_blocks((j0, j1))])
+                last = ch_back.push([(gi_ptrs[s] + d * row_bytes, g_ptr + l * row_bytes, n * row_bytes)
+                                     for s, d, l, n in plan.combine_blocks((j0, j1))])
             else:
-                last = ch.push([])
+                last = ch_back.push([])
             if live and wgrad:
                 backend.grouped_wgrad(grad_pre_t[t0:t1], input_t_fp8[t0:t1], _rel(offs, j0, j1), fc1_out, hidden, dpre_si,
                                       ms(_T.kForwardInputGroup1, _M.kScaleInv, j0), c=grad_fc1[j0:j1])
-        ch.wait(last)
+        ch_back.wait(last)
         return gi, grad_fc1, grad_fc2, None
 
 
@@ -387,12 +416,19 @@ def forward(module, input, group_sizes, is_first_microbatch, num_chunks):
     ectx = EpContext.get(input.device, module.group)
     grad_on = torch.is_grad_enabled()
     want_gi = grad_on and input.requires_grad
-    plan = ectx.plan(group_sizes, input.shape[1] * 2, num_chunks, want_gi)
     mlp.get_fp8_weights_scratchpad(is_first_microbatch)
-    st = {"mlp": mlp, "plan": plan, "ctx": ectx, "grad_enabled": grad_on,
-          "weight_cache": None if is_first_microbatch is None else mlp._fp8_weights,
-          "reuse_weights": is_first_microbatch is False}
+    cache = None if is_first_microbatch is None else mlp._fp8_weights
+    reuse = is_first_microbatch is False
     with mlp.prepare_forward(input, is_first_microbatch, mlp.num_groups * 2):
+        # The fc1 weight cast needs nothing from the other ranks: it is enqueued first and keeps the GPU busy
+        # while the host waits for the all-gather of the group sizes.
+        metas = Fp8MetaWrapper(mlp.num_groups, mlp.fp8_meta)
+        fdt = to_torch_dtype(get_fp8_te_dtype(mlp.fp8_meta["recipe"], fprop_tensor=True))
+        fc1 = cast_weight_cached(mlp.fc1_weight, fdt, want_gi, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
+                                 metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax), cache, "fc1", reuse)
+        plan = ectx.plan(group_sizes, input.shape[1] * 2, num_chunks, want_gi)
+        st = {"mlp": mlp, "plan": plan, "ctx": ectx, "grad_enabled": grad_on, "weight_cache": cache,
+              "reuse_weights": reuse, "fc1_fp8": fc1}
         if grad_on:
             return _PeerEpMlp.apply(input, mlp.fc1_weight, mlp.fc2_weight, st)
         return _PeerEpMlp.forward(None, input, mlp.fc1_weight, mlp.fc2_weight, st)

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from fp8_gmm_b200.ep_peer import PeerPlan
+from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds
 
 
 def _counts(P, E, seed, zeros=True):
@@ -63,3 +63,13 @@ def test_staggered_peer_order():
     counts = _counts(4, 8, seed=3, zeros=False)
     firsts = [PeerPlan(counts, r, 1).dispatch_blocks((0, 2))[0][0] for r in range(4)]
     assert sorted(firsts) == [0, 1, 2, 3], "every rank must start with a different destination"
+
+
+@pytest.mark.parametrize("El", [1, 2, 5, 6, 16, 32, 64])
+def test_tapered_and_explicit_chunks_partition_the_experts(El):
+    for spec in ("tapered", 3, [El]):
+        chunks = chunk_bounds(El, spec)
+        assert [j for a, b in chunks for j in range(a, b)] == list(range(El))
+    if El >= 16:
+        sizes = [b - a for a, b in chunk_bounds(El, "tapered")]
+        assert sizes[0] < max(sizes) and sizes[-1] < max(sizes)
