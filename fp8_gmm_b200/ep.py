@@ -160,15 +160,18 @@ class ExpertParallelMlp(torch.nn.Module):
     """
 
     def __init__(self, in_features, out_features, num_experts, dtype, device="cuda", activation="gelu", group=None,
-                 transport="auto", num_chunks=4):
+                 transport="auto", num_chunks=4, fp8_dispatch=True):
         """``transport``: "peer" = rows pushed by the copy engines into peer-mapped buffers, pipelined with the GEMMs
         in ``num_chunks`` chunks of experts (fp8_gmm_b200.ep_peer; one NVSwitch node, NCCL process group);
-        "nccl" = NCCL all-to-all before and after the whole local MLP; "auto" = "peer" on an NCCL group."""
+        "nccl" = NCCL all-to-all before and after the whole local MLP; "auto" = "peer" on an NCCL group.
+        ``fp8_dispatch`` (peer transport): rows are cast to FP8 on the rank that holds them, with the owning rank's
+        scale for their expert, and travel as FP8 -- the same bytes the owner would have produced, half the traffic;
+        the partial amaxes travel with them and are max-merged at the owner."""
         super().__init__()
         from .grouped_mlp import GroupedMlp
 
         assert transport in ("auto", "peer", "nccl")
-        self.transport, self.num_chunks = transport, num_chunks
+        self.transport, self.num_chunks, self.fp8_dispatch = transport, num_chunks, fp8_dispatch
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         assert num_experts % self.world == 0, "the number of experts must be divisible by the number of ranks"

@@ -62,7 +62,8 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
     spec = str(args.ep_chunks)
     chunks = spec if spec == "tapered" else int(spec) if spec.isdigit() else [int(v) for v in spec.split(",")]
     model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu",
-                                 transport=args.ep_transport, num_chunks=chunks)
+                                 transport=args.ep_transport, num_chunks=chunks,
+                                 fp8_dispatch=not args.ep_bf16_dispatch)
     with torch.no_grad():
         model.mlp.fc1_weight.normal_(0.0, 0.02)
         model.mlp.fc2_weight.normal_(0.0, 0.02)
@@ -153,7 +154,8 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
             "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp8 (e4m3 fwd / e5m2 grad, fp32 accumulate in TMEM, bf16 out)", "data": "synthetic",
             "config": {"workload": WORKLOAD_NAME, "parallelism": f"ep{world}", "experts_per_gpu": E // world,
-                       "exchange": (f"copy-engine pushes into peer memory, {args.ep_chunks} expert chunks pipelined with the GEMMs"
+                       "exchange": (f"copy-engine pushes into peer memory ({'bf16' if args.ep_bf16_dispatch else 'FP8'} dispatch, bf16 combine), "
+                                    f"{args.ep_chunks} expert chunks pipelined with the GEMMs"
                                     if args.ep_transport == "peer" and world > 1 else "NCCL all-to-all" if world > 1 else "none"),
                        "routed_rows_per_gpu": TOKENS_PER_GPU * TOPK,
                        "l2": "operands (2.1 GB of activations per GPU per exchange, 0.2-2.4 GB of weights) exceed the 126 MB L2",

@@ -172,6 +172,14 @@ class EpContext:
         self.channel_back = PeerChannel(device, group)     # combine rounds
         self.pool = _Pool(device, group)
         self.recv = None
+        self._amax_stage = None
+
+    def amax_stage(self, experts_local):
+        """(world x experts_local) fp32 in every rank's memory: row s = rank s's partial amaxes of my experts."""
+        need = self.world * experts_local * 4
+        if self._amax_stage is None or self._amax_stage.nbytes < need:
+            self._amax_stage = PeerBuffer(max(need, 4096), self.device, self.group)
+        return self._amax_stage
 
     def plan(self, group_sizes, row_bytes, num_chunks, want_grad_buffer):
         """One small all-gather: everybody's group sizes plus the result buffers each rank picked.  The gather also
@@ -231,6 +239,49 @@ class EpContext:
         return buf.tensor((rows, cols), torch.bfloat16, on_release=back)
 
 
+def _strided_rows(spec, count):
+    """The ``count`` slots of a (tensor, stride) meta view as a strided 1-D tensor view."""
+    t, stride = spec
+    return t[: (count - 1) * stride + 1: stride] if count > 0 else t[:0]
+
+
+def _gather_scales(spec, experts_local, group):
+    """Every owner's per-expert scales -> one device vector indexed by global expert (no host involvement)."""
+    local = _strided_rows(spec, experts_local).contiguous()
+    out = torch.empty(dist.get_world_size(group) * experts_local, dtype=torch.float32, device=local.device)
+    dist.all_gather_into_tensor(out, local, group=group)
+    return out
+
+
+def _quantize_at_source(ectx, plan, rows_bf16, scales_all, fp8_dtype):
+    """FP8 dispatch, source side: this rank's rows (sorted by global expert) are cast with the *owner's* scale of each
+    expert, so the bytes that travel are exactly the bytes the owner would have produced, and half as many.  Returns
+    (fp8 rows, per-global-expert amax of the rows held here)."""
+    E = plan.num_experts
+    q = torch.empty(rows_bf16.shape, dtype=fp8_dtype, device=rows_bf16.device)
+    amax_part = torch.zeros(E, dtype=torch.float32, device=rows_bf16.device)
+    backend.grouped_cast_transpose(rows_bf16, plan._send_off_l[plan.rank], q, None, None, (scales_all, 1), (amax_part, 1))
+    return q, amax_part
+
+
+def _amax_blocks(ectx, plan, amax_part, chunk):
+    """Copies that hand this rank's partial amaxes of one chunk of experts to their owners' staging rows."""
+    j0, j1 = chunk
+    El, r = plan.experts_local, plan.rank
+    stage = ectx.amax_stage(El)
+    base = amax_part.data_ptr()
+    return [(stage.ptrs[o] + (r * El + j0) * 4, base + (o * El + j0) * 4, (j1 - j0) * 4) for o in range(plan.world)]
+
+
+def _merge_amax(ectx, plan, spec, chunk):
+    """Owner side: max-merge the sources' partial amaxes of a chunk into the recipe's amax slots."""
+    j0, j1 = chunk
+    El = plan.experts_local
+    stage = ectx.amax_stage(El).tensor((plan.world, El), torch.float32)
+    view = _strided_rows(spec, j1 - j0)
+    torch.maximum(view, stage[:, j0:j1].amax(dim=0), out=view)
+
+
 def _rel(offsets, j0, j1):
     base = offsets[j0]
     return [o - base for o in offsets[j0:j1 + 1]]
@@ -262,23 +313,38 @@ class _PeerEpMlp(torch.autograd.Function):
         sizes_cpu = torch.tensor(plan.local_sizes, dtype=torch.int64)
 
         recv_ptrs = ectx.recv.ptrs
-        x_ptr = x.data_ptr()
+        fp8d = st["fp8_dispatch"]
+        ms = metas.get_meta_strided
+        if fp8d:
+            src, amax_part = _quantize_at_source(ectx, plan, x, st["x_scales"], fdt)
+            ectx.amax_stage(El)            # collective on first use: before any push refers to it
+            d_bytes = hidden               # bytes per dispatched row
+        else:
+            src, amax_part, d_bytes = x, None, row_bytes
+        x_ptr = src.data_ptr()
 
         def dispatch(chunk):
-            return ch.push([(recv_ptrs[o] + d * row_bytes, x_ptr + s * row_bytes, n * row_bytes)
-                            for o, d, s, n in plan.dispatch_blocks(chunk)])
+            blocks = [(recv_ptrs[o] + d * d_bytes, x_ptr + s * d_bytes, n * d_bytes)
+                      for o, d, s, n in plan.dispatch_blocks(chunk)]
+            if fp8d:
+                blocks += _amax_blocks(ectx, plan, amax_part, chunk)
+            return ch.push(blocks)
 
         chunks = plan.chunks
         seq = [None] * len(chunks)
         seq[0] = dispatch(chunks[0])
         # the weight casts run while the first rows are on their way
-        ms = metas.get_meta_strided
         cache, reuse = st["weight_cache"], st["reuse_weights"]
         fc1_w_fp8, fc1_w_t = st["fc1_fp8"]   # cast before the size exchange, so the GPU had work during the host sync
         fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
                                                 ms(_T.kWeightGroup2, _M.kAmax), cache, "fc2", reuse)
-        recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
-        input_fp8 = torch.empty(rows, hidden, dtype=fdt, device=dev)
+        if fp8d:
+            # the received bytes are the GEMM operand; they stay in the receive buffer until fc1 has read them
+            recv = None
+            input_fp8 = ectx.recv.tensor((rows, hidden), fdt)
+        else:
+            recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
+            input_fp8 = torch.empty(rows, hidden, dtype=fdt, device=dev)
         input_t_fp8 = torch.empty(offs[-1], hidden, dtype=fdt, device=dev) if need_wgrad else None
         pre_act = torch.empty(rows, fc1_out, dtype=torch.bfloat16, device=dev)
         act_fp8 = torch.empty(rows, ffn, dtype=fdt, device=dev)
@@ -291,11 +357,17 @@ class _PeerEpMlp(torch.autograd.Function):
                 seq[c + 1] = dispatch(chunks[c + 1])
             ch.wait(seq[c])
             r0, r1 = cumsums[j0], cumsums[j1]
+            if fp8d:
+                _merge_amax(ectx, plan, ms(_T.kInputGroup1, _M.kAmax, j0), (j0, j1))
             if r1 > r0:
-                backend.grouped_cast_transpose(
-                    recv[r0:r1], _rel(cumsums, j0, j1), input_fp8[r0:r1],
-                    input_t_fp8[offs[j0]:offs[j1]] if need_wgrad else None, _rel(offs, j0, j1),
-                    ms(_T.kInputGroup1, _M.kScale, j0), ms(_T.kInputGroup1, _M.kAmax, j0))
+                if not fp8d:
+                    backend.grouped_cast_transpose(
+                        recv[r0:r1], _rel(cumsums, j0, j1), input_fp8[r0:r1],
+                        input_t_fp8[offs[j0]:offs[j1]] if need_wgrad else None, _rel(offs, j0, j1),
+                        ms(_T.kInputGroup1, _M.kScale, j0), ms(_T.kInputGroup1, _M.kAmax, j0))
+                elif need_wgrad:
+                    backend.grouped_cast_transpose(input_fp8[r0:r1], _rel(cumsums, j0, j1), None,
+                                                   input_t_fp8[offs[j0]:offs[j1]], _rel(offs, j0, j1), None, None)
                 backend.fp8_gmm(
                     input_fp8[r0:r1], fc1_w_fp8[j0:j1], sizes_cpu[j0:j1],
                     ms(_T.kInputGroup1, _M.kScaleInv, j0), ms(_T.kWeightGroup1, _M.kScaleInv, j0),
@@ -341,17 +413,32 @@ class _PeerEpMlp(torch.autograd.Function):
         ms = metas.get_meta_strided
 
         recv_ptrs = ectx.recv.ptrs
-        dy_ptr = dy.data_ptr()
+        fp8d = st["fp8_dispatch"]
+        if fp8d:
+            # the owners' gradient scales were refreshed by prepare_backward just above: hand them round on the device
+            dy_scales = _gather_scales(ms(_T.kGradOutputGroup1, _M.kScale), El, ectx.group)
+            src, amax_part = _quantize_at_source(ectx, plan, dy, dy_scales, gdt)
+            d_bytes = hidden
+        else:
+            src, amax_part, d_bytes = dy, None, row_bytes
+        dy_ptr = src.data_ptr()
 
         def dispatch(chunk):
-            return ch.push([(recv_ptrs[o] + d * row_bytes, dy_ptr + s * row_bytes, n * row_bytes)
-                            for o, d, s, n in plan.dispatch_blocks(chunk)])
+            blocks = [(recv_ptrs[o] + d * d_bytes, dy_ptr + s * d_bytes, n * d_bytes)
+                      for o, d, s, n in plan.dispatch_blocks(chunk)]
+            if fp8d:
+                blocks += _amax_blocks(ectx, plan, amax_part, chunk)
+            return ch.push(blocks)
 
         chunks = plan.chunks
         seq = [None] * len(chunks)
         seq[0] = dispatch(chunks[0])
-        recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
-        grad_out_fp8 = torch.empty(rows, hidden, dtype=gdt, device=dev)
+        if fp8d:
+            recv = None
+            grad_out_fp8 = ectx.recv.tensor((rows, hidden), gdt)
+        else:
+            recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
+            grad_out_fp8 = torch.empty(rows, hidden, dtype=gdt, device=dev)
         grad_out_t = torch.empty(offs[-1], hidden, dtype=gdt, device=dev) if wgrad else None
         act_t = torch.empty(offs[-1], ffn, dtype=act_fp8.dtype, device=dev) if wgrad else None
         grad_pre_fp8 = torch.empty(rows, fc1_out, dtype=gdt, device=dev)
@@ -376,10 +463,16 @@ class _PeerEpMlp(torch.autograd.Function):
                 backend.grouped_cast_transpose(act_fp8[r0:r1], _rel(cumsums, j0, j1), None, act_t[t0:t1], _rel(offs, j0, j1),
                                                None, None)
             ch.wait(seq[c])
+            if fp8d:
+                _merge_amax(ectx, plan, ms(_T.kGradOutputGroup1, _M.kAmax, j0), (j0, j1))
             if live:
-                backend.grouped_cast_transpose(
-                    recv[r0:r1], _rel(cumsums, j0, j1), grad_out_fp8[r0:r1], grad_out_t[t0:t1] if wgrad else None,
-                    _rel(offs, j0, j1), ms(_T.kGradOutputGroup1, _M.kScale, j0), ms(_T.kGradOutputGroup1, _M.kAmax, j0))
+                if not fp8d:
+                    backend.grouped_cast_transpose(
+                        recv[r0:r1], _rel(cumsums, j0, j1), grad_out_fp8[r0:r1], grad_out_t[t0:t1] if wgrad else None,
+                        _rel(offs, j0, j1), ms(_T.kGradOutputGroup1, _M.kScale, j0), ms(_T.kGradOutputGroup1, _M.kAmax, j0))
+                elif wgrad:
+                    backend.grouped_cast_transpose(grad_out_fp8[r0:r1], _rel(cumsums, j0, j1), None, grad_out_t[t0:t1],
+                                                   _rel(offs, j0, j1), None, None)
                 dy_si = ms(_T.kGradOutputGroup1, _M.kScaleInv, j0)
                 if wgrad:
                     backend.grouped_wgrad(grad_out_t[t0:t1], act_t[t0:t1], _rel(offs, j0, j1), hidden, ffn, dy_si,
@@ -426,9 +519,11 @@ def forward(module, input, group_sizes, is_first_microbatch, num_chunks):
         fdt = to_torch_dtype(get_fp8_te_dtype(mlp.fp8_meta["recipe"], fprop_tensor=True))
         fc1 = cast_weight_cached(mlp.fc1_weight, fdt, want_gi, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
                                  metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax), cache, "fc1", reuse)
+        fp8d = bool(getattr(module, "fp8_dispatch", True))
+        x_scales = _gather_scales(metas.get_meta_strided(_T.kInputGroup1, _M.kScale), mlp.num_groups, module.group) if fp8d else None
         plan = ectx.plan(group_sizes, input.shape[1] * 2, num_chunks, want_gi)
         st = {"mlp": mlp, "plan": plan, "ctx": ectx, "grad_enabled": grad_on, "weight_cache": cache,
-              "reuse_weights": reuse, "fc1_fp8": fc1}
+              "reuse_weights": reuse, "fc1_fp8": fc1, "fp8_dispatch": fp8d, "x_scales": x_scales}
         if grad_on:
             return _PeerEpMlp.apply(input, mlp.fc1_weight, mlp.fc2_weight, st)
         return _PeerEpMlp.forward(None, input, mlp.fc1_weight, mlp.fc2_weight, st)

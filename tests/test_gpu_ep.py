@@ -37,8 +37,9 @@ def _worker(rank, port, errq, transport):
             xs.append(torch.randn(n, H, generator=gr).to(torch.bfloat16))
             dys.append(torch.randn(n, H, generator=gr).to(torch.bfloat16))
         El = E // WORLD
-        model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu", transport=transport,
-                                     num_chunks=2)
+        model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu",
+                                     transport=transport.split("-")[0], num_chunks=2,
+                                     fp8_dispatch=not transport.endswith("bf16"))
         with torch.no_grad():
             model.mlp.fc1_weight.copy_(w1[rank * El:(rank + 1) * El])
             model.mlp.fc2_weight.copy_(w2[rank * El:(rank + 1) * El])
@@ -47,7 +48,7 @@ def _worker(rank, port, errq, transport):
             out = model(x, _sizes(rank))
         out.backward(dys[rank].to(dev))
         fg.backend.device_status()
-        if transport == "peer":
+        if transport.startswith("peer"):
             # a second step reuses the receive buffers and the result pool: same inputs, same state -> same results
             first = (out.detach().clone(), x.grad.clone(), model.mlp.fc1_weight.grad.clone())
             del out
@@ -93,13 +94,13 @@ def _worker(rank, port, errq, transport):
         raise
 
 
-@pytest.mark.parametrize("transport", ["nccl", "peer"])
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer-bf16"])
 def test_expert_parallel_matches_single_gpu(cuda, transport):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs 2 GPUs")
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
-    port = 29900 + os.getpid() % 90 + (100 if transport == "peer" else 0)
+    port = 29900 + os.getpid() % 90 + {"nccl": 0, "peer": 100, "peer-bf16": 200}[transport]
     procs = [ctx.Process(target=_worker, args=(r, port, errq, transport)) for r in range(WORLD)]
     for p in procs:
         p.start()
