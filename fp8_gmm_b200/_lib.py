@@ -97,6 +97,10 @@ SYMBOLS = {
     "fp8gmm_grouped_wgrad_static": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_set_gemm_sm_limit": (ctypes.c_int, [ctypes.c_int]),
     "fp8gmm_set_gemm_profile_buffer": (ctypes.c_int, [c_vp, ctypes.c_size_t]),
+    "fp8gmm_moe_sort": (ctypes.c_int, [c_vp, c_i64, ctypes.c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "fp8gmm_moe_gather": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),
+    "fp8gmm_moe_scatter": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),
+    "fp8gmm_moe_rowdot": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),
     "fp8gmm_peer_alloc": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(c_vp), c_vp]),
     "fp8gmm_peer_free": (ctypes.c_int, [c_vp]),
     "fp8gmm_peer_open": (ctypes.c_int, [c_vp, ctypes.POINTER(c_vp)]),

@@ -23,6 +23,7 @@ BUILD = os.path.join(HERE, "_build")
 SOURCES = [
     ("runtime.cu", []),
     ("peer.cu", []),
+    ("routing.cu", []),
     ("pointwise.cu", ["--use_fast_math"]),
     ("pad_fusion.cu", ["--use_fast_math"]),
     ("gemm_sm100.cu", ["--use_fast_math"]),

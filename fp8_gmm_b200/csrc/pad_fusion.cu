@@ -5,6 +5,8 @@
 //   kDgelu      as kCast on x = in * dgelu_tanh(in2)
 //   kDswiglu    SwiGLU backward on in = d(act) (rows x F), in2 = [gate | up] (rows x 2F): two output halves
 //   kTranspose  fp8 (rows x cols) -> fp8 padded transpose only
+// kCast and kTranspose run in multi_pad_kernel, the two activation-backward modes in act_pad_kernel (same tile
+// shape and thread mapping, different register strategy: see there).
 // Semantics: reference csrc/multi_pad_fusion.cu:46-153 (transpose), :155-292 (cast), :294-438 (dgelu).
 //
 // Design for B200: a CTA of 256 threads owns a 128-row x 256-column tile.  Warp w, lane l loads the
@@ -73,8 +75,9 @@ __device__ __forceinline__ float dgelu_tanh(float x) {
 __device__ __forceinline__ uint32_t put_byte(uint32_t word, uint32_t b, int pos) { return word | (b << (8 * pos)); }
 
 template <int kMode, int kFormat>
-__global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspose) ? 3 : 1) multi_pad_kernel(const __grid_constant__ PadArgs args) {
-  constexpr int kHalves = (kMode == kDswiglu) ? 2 : 1;
+__global__ void __launch_bounds__(kThreads, 3) multi_pad_kernel(const __grid_constant__ PadArgs args) {
+  static_assert(kMode == kCast || kMode == kTranspose, "the activation-backward modes use act_pad_kernel");
+  constexpr int kHalves = 1;
   extern __shared__ __align__(16) uint8_t smem_t[];  // [col][kTileRows bytes of rows], 16-byte chunks XOR-swizzled
   __shared__ float staging[kThreads / 32];
 
@@ -87,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspo
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rows = d.rows, cols = d.cols;
   const int64_t ld_in = cols;                                   // row pitch of `in`
-  const int64_t ld_io = (kMode == kDswiglu) ? 2 * (int64_t)cols : cols;  // row pitch of in2 (dswiglu) and of `out`
+  const int64_t ld_io = cols;                                   // row pitch of `out`
   const float scale = (kMode == kTranspose) ? 1.f : (d.scale ? *d.scale : 1.0f);
   const int col0 = tile_col + lane * 8;
   const int row0 = tile_row + warp * 16;
@@ -138,7 +141,6 @@ __global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspo
     }
   } else {
     const uint16_t* in = static_cast<const uint16_t*>(d.in);
-    const uint16_t* in2 = static_cast<const uint16_t*>(d.in2);
     // all 16 row loads of `in` are issued before the first use: 256 bytes per thread in flight
     uint4 pre[16];
 #pragma unroll
@@ -149,9 +151,9 @@ __global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspo
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int row = row0 + i;
-      float x[8], y[8], z[8];  // x: in; y: in2 (dgelu: pre-act, dswiglu: gate); z: dswiglu up
+      float x[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = y[j] = z[j] = 0.f;
+      for (int j = 0; j < 8; ++j) x[j] = 0.f;
       const bool live = row < rows && col0 < cols;
       if (live) {
         if (fast_io) {
@@ -159,44 +161,18 @@ __global__ void __launch_bounds__(kThreads, (kMode == kCast || kMode == kTranspo
           const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) x[2 * j] = bf16_lo(w[j]), x[2 * j + 1] = bf16_hi(w[j]);
-          if (kMode == kDgelu || kMode == kDswiglu) {
-            const uint4 g = ld_stream16(in2 + (int64_t)row * ld_io + col0);
-            const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[2 * j] = bf16_lo(gw[j]), y[2 * j + 1] = bf16_hi(gw[j]);
-          }
-          if (kMode == kDswiglu) {
-            const uint4 u = ld_stream16(in2 + (int64_t)row * ld_io + cols + col0);
-            const uint32_t uw[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) z[2 * j] = bf16_lo(uw[j]), z[2 * j + 1] = bf16_hi(uw[j]);
-          }
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             if (col0 + j < cols) {
               x[j] = __uint_as_float((uint32_t)in[(int64_t)row * ld_in + col0 + j] << 16);
-              if (kMode == kDgelu || kMode == kDswiglu)
-                y[j] = __uint_as_float((uint32_t)in2[(int64_t)row * ld_io + col0 + j] << 16);
-              if (kMode == kDswiglu) z[j] = __uint_as_float((uint32_t)in2[(int64_t)row * ld_io + cols + col0 + j] << 16);
             }
         }
       }
-      float v0[8], v1[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (kMode == kCast) {
-          v0[j] = x[j];
-        } else if (kMode == kDgelu) {
-          v0[j] = x[j] * dgelu_tanh(y[j]);
-        } else {  // kDswiglu: d gate = dy * up * sigmoid'(...) form, d up = dy * silu(gate)
-          const float s = 1.f / (1.f + __expf(-y[j]));
-          v0[j] = x[j] * z[j] * (s * (1.f + y[j] * (1.f - s)));
-          v1[j] = x[j] * (y[j] * s);
-        }
-        amax = fmaxf(fabsf(v0[j]), amax);
-        if (kMode == kDswiglu) amax = fmaxf(fabsf(v1[j]), amax);
-      }
+      for (int j = 0; j < 8; ++j) amax = fmaxf(fabsf(x[j]), amax);
+      const float* v0 = x;
+      const float* v1 = x;
 #pragma unroll
       for (int h = 0; h < kHalves; ++h) {
         const float* v = h == 0 ? v0 : v1;

@@ -40,7 +40,7 @@ def _timed(fn, steps, world):
     return float(secs)
 
 
-def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
+def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu, E2EPipeline):
     import fp8_gmm_b200 as fg
     from fp8_gmm_b200 import backend, ep
 
@@ -80,12 +80,15 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
         out.backward(dy_dev)
         return out
 
-    def step_e2e():
-        x_dev.data.copy_(x_host, non_blocking=True)
-        dy_dev.copy_(dy_host, non_blocking=True)
-        out = step()
-        out_host.copy_(out.detach(), non_blocking=True)
-        gi_host.copy_(x_dev.grad, non_blocking=True)
+    def step_on(x_in, dy_in):
+        model.mlp.fc1_weight.grad = None
+        model.mlp.fc2_weight.grad = None
+        with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+            out = model(x_in, sizes)
+        out.backward(dy_in)
+        return out, x_in.grad
+
+    e2e = E2EPipeline(step_on, x_host, dy_host, out_host, gi_host, dev)
 
     warmup = max(args.warmup, 3)
     sampler = ClockSampler(local_rank)
@@ -116,9 +119,8 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu):
     gemm_ms = sum(s.elapsed_time(e) for s, e, _ in timings)
     gemm_flops_local = sum(f for _, _, f in timings)
 
-    for _ in range(2):
-        step_e2e()
-    secs_e2e = _timed(step_e2e, args.steps, world)
+    e2e.run(2)
+    secs_e2e = _timed(lambda: e2e.run(args.steps), 1, world)
 
     # the same local problem without the exchange (what this rank's experts compute), for the EP efficiency figure
     local_secs = None

@@ -4,8 +4,9 @@ Where fp8_gmm_b200.ep moves rows with NCCL all-to-all around an unchanged Groupe
 then exchange), this module splits a rank's experts into chunks and overlaps the exchange of one chunk with the
 GEMMs of another:
 
-    copy engines :  D0   D1        C0  D2        C1  D3        C2        C3
-    SMs          :  w-cast   [cast fc1 fc2]0   [cast fc1 fc2]1   [...]2   [...]3
+    copy engines, dispatch channel :  D0 D1 D2 D3
+    copy engines, combine channel  :           C0                C1                C2       C3
+    SMs                            :  w-cast [cast fc1 fc2]0   [cast fc1 fc2]1   [...]2   [...]3
 
 ``Dk`` pushes the rows of chunk k's experts from every rank straight into their place in the owner's
 expert-major receive buffer (one device-to-device copy per (destination expert) block, so no permutation kernel
@@ -330,10 +331,11 @@ class _PeerEpMlp(torch.autograd.Function):
                 blocks += _amax_blocks(ectx, plan, amax_part, chunk)
             return ch.push(blocks)
 
+        # Every dispatch round is queued now: the rows are ready, and a round that waited for earlier chunks'
+        # GEMMs (with which it has nothing to do) would start late and then share the links with the combine rounds.
         chunks = plan.chunks
-        seq = [None] * len(chunks)
-        seq[0] = dispatch(chunks[0])
-        # the weight casts run while the first rows are on their way
+        seq = [dispatch(chunk) for chunk in chunks]
+        # the fc2 weight cast runs while the first rows are on their way
         cache, reuse = st["weight_cache"], st["reuse_weights"]
         fc1_w_fp8, fc1_w_t = st["fc1_fp8"]   # cast before the size exchange, so the GPU had work during the host sync
         fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
@@ -353,8 +355,6 @@ class _PeerEpMlp(torch.autograd.Function):
         out_ptrs = [ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)]
         last = None
         for c, (j0, j1) in enumerate(chunks):
-            if c + 1 < len(chunks):
-                seq[c + 1] = dispatch(chunks[c + 1])
             ch.wait(seq[c])
             r0, r1 = cumsums[j0], cumsums[j1]
             if fp8d:
@@ -431,8 +431,7 @@ class _PeerEpMlp(torch.autograd.Function):
             return ch.push(blocks)
 
         chunks = plan.chunks
-        seq = [None] * len(chunks)
-        seq[0] = dispatch(chunks[0])
+        seq = [dispatch(chunk) for chunk in chunks]   # all rounds up front, as in forward
         if fp8d:
             recv = None
             grad_out_fp8 = ectx.recv.tensor((rows, hidden), gdt)
@@ -453,8 +452,6 @@ class _PeerEpMlp(torch.autograd.Function):
             gi_ptrs = [ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)]
         last = None
         for c, (j0, j1) in enumerate(chunks):
-            if c + 1 < len(chunks):
-                seq[c + 1] = dispatch(chunks[c + 1])
             r0, r1 = cumsums[j0], cumsums[j1]
             t0, t1 = offs[j0], offs[j1]
             live = r1 > r0

@@ -127,11 +127,16 @@ class PeerChannel:
         if lanes == 1:
             check(lib.fp8gmm_peer_copy_blocks(arr, len(blocks), s), "peer_copy_blocks")
         else:
+            # consecutive blocks usually go to the same peer: deal them out in runs, so that the lanes work on
+            # different peers at the same time
             streams = [self.stream] + self.side
             for st in self.side:
                 st.wait_stream(self.stream)
+            run = -(-len(blocks) // lanes)
             for k, st in enumerate(streams):
-                part = blocks[k::lanes]
+                part = blocks[k * run:(k + 1) * run]
+                if not part:
+                    continue
                 sub = (CopyBlock * len(part))()
                 for i, (dst, src, nbytes) in enumerate(part):
                     sub[i].dst, sub[i].src, sub[i].bytes = dst, src, nbytes

@@ -312,6 +312,32 @@ int fp8gmm_delayed_scaling_update(float* amax_history, float* scale, float* scal
                                   float fp8_max, float margin, int algo, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Router-side row permutation of an MoE block: the steps either side of the grouped GEMMs that the reference's
+ * example takes from megablocks (reference fp8_gmm/example.py:26-32 sort / histogram / inclusive_cumsum,
+ * :52,:87,:118 gather, :59,:92,:121 scatter).  All pointers are device memory; rows are bf16.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Stable counting sort of n = tokens * top_k expert ids (int32, values in [0, num_experts)):
+ *   indices[i]  flat (token, slot) position held by sorted row i        bin_ids[i]  expert of sorted row i
+ *   inverse[p]  sorted row of flat position p                           tokens_per_expert[e], bins[e] = inclusive cumsum
+ * Equal ids keep their order, so the result is deterministic. */
+int fp8gmm_moe_sort(const int32_t* expert_ids, int64_t n, int num_experts, int32_t* indices, int32_t* bin_ids,
+                    int32_t* inverse, int64_t* bins, int64_t* tokens_per_expert, void* stream);
+
+/* out[i, :] = x[indices[i] / top_k, :] for i < rows, multiplied by weights[indices[i]] when weights != NULL. */
+int fp8gmm_moe_gather(const void* x, const int32_t* indices, const float* weights, int top_k, int64_t rows, int64_t cols,
+                      void* out, void* stream);
+
+/* out[t, :] = sum_k weights[t*top_k + k] * x[inverse[t*top_k + k], :] (weights NULL = 1), fp32 accumulation with k
+ * ascending, one rounding to bf16. */
+int fp8gmm_moe_scatter(const void* x, const int32_t* inverse, const float* weights, int top_k, int64_t tokens, int64_t cols,
+                       void* out, void* stream);
+
+/* d_weights[p] = dot(grad[p / top_k, :], x[inverse[p], :]) for p < n: the gradient of the scatter w.r.t. its weights. */
+int fp8gmm_moe_rowdot(const void* grad, const void* x, const int32_t* inverse, int top_k, int64_t n, int64_t cols,
+                      float* d_weights, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Peer-memory transport for the expert-parallel row exchange (dispatch / combine between the GPUs of one
  * NVSwitch node).  No counterpart in the reference, which is single-GPU apart from one all-reduce
  * (reference fp8_gmm/grouped_mlp.py:300-303) and permutes rows on one device (fp8_gmm/example.py:52-59).

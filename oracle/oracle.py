@@ -317,3 +317,37 @@ def current_scale(x, dtype):
     CPU-runnable config."""
     a = amax_merge(x)
     return FP8_MAX[dtype] / a if a > 0 and math.isfinite(a) else 1.0
+
+
+# ------------------------------------------------------------------------------------------------
+# Router-side permutation (reference fp8_gmm/example.py:26-32,52,59: megablocks sort / histogram /
+# inclusive_cumsum / gather / scatter, restated from their call sites; megablocks itself is absent: parity unpinned)
+# ------------------------------------------------------------------------------------------------
+def moe_sort(top_expert, n_experts):
+    """Stable sort of the flat expert ids: (indices, bin_ids, bins, tokens_per_expert, inverse)."""
+    ids = top_expert.reshape(-1).to(torch.int64)
+    bin_ids, indices = torch.sort(ids, stable=True)
+    hist = torch.bincount(ids, minlength=n_experts)
+    inverse = torch.empty_like(indices)
+    inverse[indices] = torch.arange(ids.numel())
+    return indices, bin_ids, torch.cumsum(hist, 0), hist, inverse
+
+
+def moe_gather(x, indices, top_k, weights=None):
+    """out[i] = x[indices[i] // top_k] (times weights[indices[i]], product rounded once to bf16)."""
+    rows = x[indices // top_k]
+    if weights is None:
+        return rows.clone()
+    return (rows.float() * weights.reshape(-1).float()[indices, None]).to(x.dtype)
+
+
+def moe_scatter(x, inverse, top_k, weights=None):
+    """out[t] = sum_k w[t, k] * x[inverse[t * top_k + k]]: fp32 fused multiply-adds with k ascending, one rounding."""
+    tokens = inverse.numel() // top_k
+    acc = torch.zeros(tokens, x.shape[1], dtype=torch.float64)
+    w = torch.ones(tokens * top_k) if weights is None else weights.reshape(-1).float()
+    for k in range(top_k):
+        p = torch.arange(tokens) * top_k + k
+        # a float64 multiply-add rounded to float32 equals the fused fp32 multiply-add of the kernel
+        acc = (w[p, None].double() * x[inverse[p]].double() + acc).float().double()
+    return acc.float().to(x.dtype)

@@ -54,3 +54,21 @@ def test_dtype_maps_and_recipe_formats():
     with recipe.fp8_autocast(enabled=True, fp8_recipe=recipe.DelayedScaling(amax_history_len=16)):
         assert recipe.is_fp8_enabled() and recipe.get_fp8_recipe().amax_history_len == 16
     assert not recipe.is_fp8_enabled()
+
+
+def test_router_oracle_round_trip():
+    """oracle.moe_sort / moe_gather / moe_scatter: gathering and scattering with unit weights and top_k = 1 is the
+    identity; with top_k > 1 every token gets the sum of its copies."""
+    from oracle import oracle as O
+
+    g = torch.Generator().manual_seed(0)
+    tokens, top_k, E, H = 50, 3, 7, 16
+    ids = torch.randint(0, E, (tokens * top_k,), generator=g)
+    indices, bin_ids, bins, hist, inverse = O.moe_sort(ids, E)
+    assert torch.equal(bin_ids, ids[indices]) and (bin_ids[1:] >= bin_ids[:-1]).all()
+    assert int(bins[-1]) == tokens * top_k and torch.equal(hist, torch.bincount(ids, minlength=E))
+    x = torch.randn(tokens, H, generator=g).to(torch.bfloat16)
+    rows = O.moe_gather(x, indices, top_k)
+    assert torch.equal(rows[inverse].reshape(tokens, top_k, H)[:, 0], x)
+    out = O.moe_scatter(rows, inverse, top_k)
+    assert torch.allclose(out.float(), 3 * x.float(), rtol=1e-2, atol=1e-2)
