@@ -7,17 +7,20 @@
 // Kernel shape
 //   * one persistent CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM
 //     owner), warps 2-5 = epilogue (each owns the 32 TMEM lanes its warp id selects);
-//   * output tile 128 x 256, K step 128 bytes (one 128-byte swizzle atom), 4-stage shared-memory ring
-//     (48 KiB per stage: A 128x128 B + B 256x128 B, both K-major, written by TMA with SWIZZLE_128B);
+//   * output tile 128 x 256 per CTA, or 256 x 256 per CTA pair (cta_group::2, the default for large groups);
+//     K step 128 bytes (one 128-byte swizzle atom); shared-memory ring of 4 stages x 48 KiB (single CTA) or
+//     6 stages x 32 KiB (pair: every CTA loads its own 128 A rows and 128 B rows), K-major, written by TMA
+//     with SWIZZLE_128B;
 //   * tcgen05.mma.cta_group::1.kind::f8f6f4, M=128 N=256 K=32, fp32 accumulators in TMEM; the 512 TMEM
 //     columns hold two accumulators so the epilogue of tile i overlaps the main loop of tile i+1;
-//   * epilogue: tcgen05.ld -> (a_scale_inv*b_scale_inv) -> bf16 -> predicated 16-byte stores (a tile may
-//     straddle the end of its group, so rows are masked); optional fused activation (GELU or SwiGLU)
-//     that also emits the e4m3 activation and its amax;
+//   * epilogue: tcgen05.ld -> (a_scale_inv*b_scale_inv) -> bf16; full 32-row slabs are staged in shared memory
+//     (SWIZZLE_128B boxes) and written by TMA stores, slabs that straddle the end of their group fall back to
+//     predicated 16-byte stores; optional fused activation (GELU or SwiGLU) that also emits the e4m3
+//     activation and its amax;
 //   * device-side scheduler: every role walks the same static tile sequence blockIdx.x + i*gridDim.x and
 //     decodes (group, m-tile, n-tile) from prefix sums held in the kernel parameter block.  Tiles are
-//     ordered group-major and, inside a group, in super-rows of 32 m-tiles with m fastest, so the ~148
-//     concurrently running tiles share operand tiles through L2;
+//     ordered group-major and, inside a group, in super-rows of 4096 rows (2048 for long contractions) with
+//     m fastest, so the concurrently running tiles share operand tiles through L2;
 //   * no cluster launch and no multicast: every CTA loads its own operands.
 // Two addressing modes share the kernel: "rows" (forward/dgrad: groups are row blocks of one A matrix,
 // B is (G,N,K)) and "wgrad" (each group has its own pair of TMA descriptors in global memory because the
