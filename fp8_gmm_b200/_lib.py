@@ -95,6 +95,7 @@ SYMBOLS = {
     "fp8gmm_wgrad_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int]),
     "fp8gmm_grouped_wgrad": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_grouped_wgrad_static": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
+    "fp8gmm_grouped_wgrad_rowmajor": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_set_gemm_sm_limit": (ctypes.c_int, [ctypes.c_int]),
     "fp8gmm_set_gemm_profile_buffer": (ctypes.c_int, [c_vp, ctypes.c_size_t]),
     "fp8gmm_moe_sort": (ctypes.c_int, [c_vp, c_i64, ctypes.c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),

@@ -10,6 +10,7 @@ functions are the allocation-free fast forms the modules use: one base tensor pl
 instead of Python lists of per-group views.
 """
 import ctypes
+import os
 
 import torch
 
@@ -18,6 +19,10 @@ from ._lib import BlockedCastArgs, GemmArgs, GroupedCastArgs, ScaleMulDesc, Tens
 from .utils import FP8_FORMAT_CODE
 
 _FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+# Weight gradients read the row-major FP8 activations directly (grouped_wgrad_rowmajor), so the modules make no
+# padded-transposed copies.  FP8GMM_WGRAD=transposed selects the reference's dataflow instead (padded transposes
+# written by the cast kernels, reference fp8_gmm/grouped_linear.py:32-52,133-149, consumed by grouped_wgrad).
+WGRAD_ROWMAJOR = os.environ.get("FP8GMM_WGRAD", "rowmajor") != "transposed"
 ACT_NONE, ACT_GELU, ACT_SWIGLU = 0, 1, 2
 _ACT_CODE = {None: 0, "none": 0, "gelu": 1, "swiglu": 2}
 
@@ -479,6 +484,36 @@ def grouped_wgrad(a_t, b_t, t_offsets, n, k, a_scale_invs, b_scale_invs, c=None)
     args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
     with _Timed(2.0 * a_t.numel() * k):  # a_t holds (padded rows) x n elements
         check(lib.fp8gmm_grouped_wgrad(ctypes.byref(args), _stream()), "grouped_wgrad")
+    del keep
+    return c
+
+
+def grouped_wgrad_rowmajor(dy, x, row_offsets, a_scale_invs, b_scale_invs, c=None):
+    """All weight gradients in one launch from the row-major FP8 activations, no transposed copies:
+    ``c[g] (n, k) = (dy[rows of g] * sa[g])^T (x[rows of g] * sb[g])`` with dy (sum m, n), x (sum m, k) and
+    ``row_offsets`` the host prefix sums of the group sizes (any sizes; empty groups give zeros).  Same result as
+    ``grouped_wgrad`` on the padded transposes of the same rows (see fp8gmm_grouped_wgrad_rowmajor)."""
+    G = len(row_offsets) - 1
+    _cuda_2d(dy, "dy", _FP8)
+    _cuda_2d(x, "x", _FP8)
+    _require(dy.dim() == 2 and x.dim() == 2 and dy.shape[0] == x.shape[0], "grouped_wgrad_rowmajor: row counts differ")
+    n, k = dy.shape[1], x.shape[1]
+    if c is None:
+        c = torch.empty(G, n, k, dtype=torch.bfloat16, device=dy.device)
+    _require(tuple(c.shape) == (G, n, k) and c.dtype == torch.bfloat16 and c.is_contiguous(), "grouped_wgrad_rowmajor: bad output")
+    args = WgradArgs()
+    args.a_t, args.b_t, args.c = dy.data_ptr(), x.data_ptr(), c.data_ptr()
+    to, keep = _i64_array(row_offsets)
+    args.t_offsets = to
+    args.num_groups, args.n, args.k = G, n, k
+    args.a_format, args.b_format = _fp8_code(dy.dtype), _fp8_code(x.dtype)
+    sa, sb = _strided(a_scale_invs, G), _strided(b_scale_invs, G)
+    args.a_scale_inv, args.a_scale_inv_stride = sa.ptr, sa.stride
+    args.b_scale_inv, args.b_scale_inv_stride = sb.ptr, sb.stride
+    ws = _workspace(dy.device, lib.fp8gmm_wgrad_workspace_bytes(G))
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    with _Timed(2.0 * dy.shape[0] * n * k):
+        check(lib.fp8gmm_grouped_wgrad_rowmajor(ctypes.byref(args), _stream()), "grouped_wgrad_rowmajor")
     del keep
     return c
 

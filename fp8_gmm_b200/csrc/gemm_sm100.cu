@@ -79,6 +79,7 @@ struct GemmParams {
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
   int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
+  int mn_major;        // kModeWgrad only: operands are row-major (rows x features) slices, i.e. MN-major for the MMA
   int super_tiles;     // m-tiles per super-row of the tile order (see decode_tile)
   int tma_store;       // 1: full 32-row slabs of a tile leave through shared memory + TMA stores (map_c is valid)
   int mode;
@@ -230,6 +231,21 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Shared-memory matrix descriptor for an MN-major operand tile: TMA wrote [contraction rows][128 bytes of the M/N
+// dimension] with SWIZZLE_128B, so a swizzle atom is 8 contraction rows x 128 M/N bytes (1024 bytes).  Stride byte
+// offset = distance between consecutive 8-row groups along the contraction (1024); leading byte offset = distance
+// between consecutive 128-byte blocks along M/N (only used when the operand is wider than 128, i.e. the 256-wide B
+// of the single-CTA kernel, whose second block is a second TMA box).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>(1024 >> 4) << 32;
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
@@ -448,17 +464,21 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
           if (ok) {
             const uint32_t sa = tiles_addr + stage * kStageBytes;
             const uint32_t sb = sa + kTileABytes;
+            // K-major operands: x = contraction offset, y = operand row.  MN-major (row-major slices of the
+            // activations): x = feature offset, y = contraction row; the box is 128 x 128 bytes either way.
+            const int kx = kb * kBlockK;
+            const bool mn = p.mn_major != 0;
             if (kCtas == 1) {
               mbar_expect_tx(full_bar(stage), kStageBytes);
-              tma_load_2d(sa, map_a, full_bar(stage), kb * kBlockK, ya);
-              tma_load_2d(sb, map_b, full_bar(stage), kb * kBlockK, yb0);
-              tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), kb * kBlockK, yb1);
+              tma_load_2d(sa, map_a, full_bar(stage), mn ? ya : kx, mn ? kx : ya);
+              tma_load_2d(sb, map_b, full_bar(stage), mn ? yb0 : kx, mn ? kx : yb0);
+              tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), mn ? yb1 : kx, mn ? kx : yb1);
             } else {
               // both CTAs credit the leader's barrier; the leader arms it for the bytes of both
               const uint32_t bar = full0_leader + 8u * stage;
               if (leader) mbar_expect_tx(full_bar(stage), 2 * kStageBytes);
-              tma_load_2d_pair(sa, map_a, bar, kb * kBlockK, ya);
-              tma_load_2d_pair(sb, map_b, bar, kb * kBlockK, yb_mine);
+              tma_load_2d_pair(sa, map_a, bar, mn ? ya : kx, mn ? kx : ya);
+              tma_load_2d_pair(sb, map_b, bar, mn ? yb_mine : kx, mn ? kx : yb_mine);
             }
           }
           if (++stage == kStages) {
@@ -483,8 +503,11 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       long long wait_full = 0, wait_tempty = 0, issue = 0;
       const long long t_begin = p.profile ? clock64() : 0;
       const unsigned long long ns_begin = p.profile ? global_ns() : 0;
-      const uint64_t desc_a0 = make_smem_desc(tiles_addr);
-      const uint64_t desc_b0 = make_smem_desc(tiles_addr + kTileABytes);
+      const bool mn = p.mn_major != 0;
+      const uint64_t desc_a0 = mn ? make_smem_desc_mn(tiles_addr, 16) : make_smem_desc(tiles_addr);
+      const uint64_t desc_b0 = mn ? make_smem_desc_mn(tiles_addr + kTileABytes, kTileBBytes / 2) : make_smem_desc(tiles_addr + kTileABytes);
+      // one MMA consumes 32 contraction bytes: 32 bytes along a K-major row, or 32 rows of 128 bytes (MN-major)
+      const uint64_t k_step = mn ? (32ull * 128ull) >> 4 : 32ull >> 4;
       const uint32_t idesc = p.idesc;
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
         const TileInfo t = decode_tile<kCtas>(p, tile, rank);
@@ -505,11 +528,11 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
           const uint64_t db = desc_b0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
 #pragma unroll
           for (int k = 0; k < kBlockK / 32; ++k) {
-            // advance both descriptors by 32 bytes (>>4 = 2) along K inside the swizzle atom
+            // advance both descriptors by one MMA's worth of contraction (k_step is in 16-byte units)
             if (kCtas == 1)
-              umma_f8(tmem_d, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_f8(tmem_d, da + k_step * k, db + k_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
             else
-              umma_f8_pair(tmem_d, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_f8_pair(tmem_d, da + k_step * k, db + k_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           if (kCtas == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage));
           if (p.profile) {
@@ -857,15 +880,16 @@ bool tma_epilogue_enabled() {
   return !(e != nullptr && e[0] == 'd');
 }
 
-uint32_t make_idesc(int a_format, int b_format, int ctas) {
+uint32_t make_idesc(int a_format, int b_format, int ctas, bool mn_major = false) {
   // tcgen05 instruction descriptor, kind::f8f6f4: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format
-  // (0 = e4m3, 1 = e5m2), bits 15/16 = 0 (both operands K-major), [17,23) N >> 3, [24,29) M >> 4.
+  // (0 = e4m3, 1 = e5m2), bits 15/16 = A / B major (0 = K-major, 1 = MN-major), [17,23) N >> 3, [24,29) M >> 4.
   uint32_t d = 0;
   d |= 1u << 4;
   d |= static_cast<uint32_t>(a_format) << 7;
   d |= static_cast<uint32_t>(b_format) << 10;
   d |= static_cast<uint32_t>(kBlockN >> 3) << 17;
   d |= static_cast<uint32_t>((kBlockM * ctas) >> 4) << 24;  // a CTA pair issues M = 256
+  if (mn_major) d |= (1u << 15) | (1u << 16);               // A and B are MN-major ("transposed") in shared memory
   return d;
 }
 
@@ -1088,6 +1112,88 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
   p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
+  if (tma_epilogue_enabled()) {
+    const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
+    if (rc_map != FP8GMM_OK) return rc_map;
+    p.tma_store = 1;
+  }
+  return launch(p, ctas, s);
+}
+
+
+// Weight gradients straight from the row-major FP8 activations: C_g (n x k) = dY_g^T X_g with dY_g = rows
+// [offsets[g], offsets[g+1]) of a (sum m x n) matrix and X_g the same rows of a (sum m x k) matrix.  Seen from the
+// MMA both operands are MN-major (the feature dimension is contiguous, the contraction runs over rows), which
+// tcgen05 takes through the major bits of the instruction descriptor -- so no padded-transposed copies of the
+// activations are needed at all.  One tensor map per group and operand bounds the group's rows, and TMA zero-fills
+// the rows past its end, so group sizes need no padding either.
+int fp8gmm_grouped_wgrad_rowmajor(const fp8gmm_wgrad_args* a, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(a != nullptr, "grouped_wgrad_rowmajor: NULL arguments");
+  FP8GMM_CHECK_ARG(a->num_groups >= 0 && a->num_groups <= kMaxGroups, "grouped_wgrad_rowmajor: num_groups %d outside [0, %d]",
+                   a->num_groups, kMaxGroups);
+  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_wgrad_rowmajor: bad fp8 format");
+  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
+                   "grouped_wgrad_rowmajor: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n, (long long)a->k);
+  if (a->num_groups == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "grouped_wgrad_rowmajor: NULL pointer");
+  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_wgrad_rowmajor: NULL scale_inv pointer");
+  FP8GMM_CHECK_ARG(a->workspace != nullptr && a->workspace_bytes >= fp8gmm_wgrad_workspace_bytes(a->num_groups),
+                   "grouped_wgrad_rowmajor: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes,
+                   fp8gmm_wgrad_workspace_bytes(a->num_groups));
+  FP8GMM_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 128 == 0, "grouped_wgrad_rowmajor: workspace must be 128-byte aligned");
+  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
+                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0, "grouped_wgrad_rowmajor: operand pointers must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int ctas = forced_ctas();
+  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
+  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
+  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
+  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad_rowmajor: problem too large");
+  std::vector<CUtensorMap> maps(static_cast<size_t>(a->num_groups) * 2);
+  memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
+  p.tile_start[0] = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
+    const int64_t len = o1 - o0;
+    FP8GMM_CHECK_ARG(len >= 0 && o1 <= INT32_MAX - 1024, "grouped_wgrad_rowmajor: group %d has a negative or oversized row range", g);
+    p.row_start[g] = static_cast<int>(o0);
+    p.row_start[g + 1] = static_cast<int>(o1);
+    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
+    if (len > 0) {
+      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "grouped_wgrad_rowmajor: NULL operand pointer");
+      // rows x features bytes, row pitch = features: the same encoder as for K-major operands (box 128 rows x 128 bytes)
+      int rc = encode_map(&maps[2 * g], static_cast<const char*>(a->a_t) + o0 * a->n, static_cast<uint64_t>(len),
+                          static_cast<uint64_t>(a->n));
+      if (rc != FP8GMM_OK) return rc;
+      rc = encode_map(&maps[2 * g + 1], static_cast<const char*>(a->b_t) + o0 * a->k, static_cast<uint64_t>(len),
+                      static_cast<uint64_t>(a->k));
+      if (rc != FP8GMM_OK) return rc;
+    }
+  }
+  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(a->workspace, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
+  p.maps = static_cast<const CUtensorMap*>(a->workspace);
+  p.c = static_cast<uint16_t*>(a->c);
+  p.sa = a->a_scale_inv;
+  p.sb = a->b_scale_inv;
+  p.sa_stride = a->a_scale_inv_stride;
+  p.sb_stride = a->b_scale_inv_stride;
+  p.ldc = a->k;
+  p.status = device_status_word();
+  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_wgrad_rowmajor: cannot resolve the device status word");
+  p.mode = kModeWgrad;
+  p.mn_major = 1;
+  p.activation = FP8GMM_ACT_NONE;
+  p.num_groups = a->num_groups;
+  p.n = static_cast<int>(a->k);
+  p.m_fixed = static_cast<int>(a->n);
+  p.k = 0;
+  p.tiles_n = static_cast<int>(tiles_n);
+  p.total_tiles = p.tile_start[a->num_groups];
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas, true);
   p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
   if (tma_epilogue_enabled()) {
     const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));

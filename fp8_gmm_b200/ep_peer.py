@@ -301,7 +301,8 @@ class _PeerEpMlp(torch.autograd.Function):
         need_wgrad = grad_on and fc1_weight.requires_grad
         need_dgrad = grad_on and x.requires_grad
         El = plan.experts_local
-        _, padded, cumsums, padded_cumsums = cumsum_group_sizes(plan.local_sizes, need_padding=need_wgrad)
+        need_t = need_wgrad and not backend.WGRAD_ROWMAJOR   # padded transposes only for the reference's wgrad dataflow
+        _, padded, cumsums, padded_cumsums = cumsum_group_sizes(plan.local_sizes, need_padding=need_t)
         offs = padded_cumsums if padded else cumsums
         rows = cumsums[-1]
         metas = Fp8MetaWrapper(El, fp8_meta)
@@ -341,14 +342,17 @@ class _PeerEpMlp(torch.autograd.Function):
         fc1_w_fp8, fc1_w_t = st["fc1_fp8"]   # cast before the size exchange, so the GPU had work during the host sync
         fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
                                                 ms(_T.kWeightGroup2, _M.kAmax), cache, "fc2", reuse)
+        keep_rows = need_wgrad and not need_t     # the row-major FP8 input is the fc1 wgrad operand: it must outlive forward
         if fp8d:
-            # the received bytes are the GEMM operand; they stay in the receive buffer until fc1 has read them
+            # the received bytes are the GEMM operand as they lie in the receive buffer
             recv = None
             input_fp8 = ectx.recv.tensor((rows, hidden), fdt)
+            input_keep = torch.empty(rows, hidden, dtype=fdt, device=dev) if keep_rows else None
         else:
             recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
             input_fp8 = torch.empty(rows, hidden, dtype=fdt, device=dev)
-        input_t_fp8 = torch.empty(offs[-1], hidden, dtype=fdt, device=dev) if need_wgrad else None
+            input_keep = input_fp8 if keep_rows else None
+        input_t_fp8 = torch.empty(offs[-1], hidden, dtype=fdt, device=dev) if need_t else None
         pre_act = torch.empty(rows, fc1_out, dtype=torch.bfloat16, device=dev)
         act_fp8 = torch.empty(rows, ffn, dtype=fdt, device=dev)
         out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
@@ -364,11 +368,14 @@ class _PeerEpMlp(torch.autograd.Function):
                 if not fp8d:
                     backend.grouped_cast_transpose(
                         recv[r0:r1], _rel(cumsums, j0, j1), input_fp8[r0:r1],
-                        input_t_fp8[offs[j0]:offs[j1]] if need_wgrad else None, _rel(offs, j0, j1),
+                        input_t_fp8[offs[j0]:offs[j1]] if need_t else None, _rel(offs, j0, j1),
                         ms(_T.kInputGroup1, _M.kScale, j0), ms(_T.kInputGroup1, _M.kAmax, j0))
-                elif need_wgrad:
+                elif need_t:
                     backend.grouped_cast_transpose(input_fp8[r0:r1], _rel(cumsums, j0, j1), None,
                                                    input_t_fp8[offs[j0]:offs[j1]], _rel(offs, j0, j1), None, None)
+                elif keep_rows:
+                    # the receive buffer is reused by the next exchange: keep the rows for the fc1 weight gradient
+                    input_keep[r0:r1].copy_(input_fp8[r0:r1])
                 backend.fp8_gmm(
                     input_fp8[r0:r1], fc1_w_fp8[j0:j1], sizes_cpu[j0:j1],
                     ms(_T.kInputGroup1, _M.kScaleInv, j0), ms(_T.kWeightGroup1, _M.kScaleInv, j0),
@@ -387,7 +394,9 @@ class _PeerEpMlp(torch.autograd.Function):
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
             # backward never runs
             ctx.gi = ectx.result_tensor(plan.gi_ids[plan.rank], plan.rows_own, hidden) if need_dgrad else None
-            ctx.save_for_backward(input_t_fp8, fc1_w_t, fc2_w_t, pre_act, act_fp8 if need_wgrad else None)
+            ctx.save_for_backward(input_t_fp8 if need_t else input_keep, fc1_w_t, fc2_w_t, pre_act,
+                                  act_fp8 if need_wgrad else None)
+            ctx.need_t = need_t
             metas.set_forward_scale_inv_cloned()
             ctx.metas, ctx.st = metas, st
             ctx.cumsums, ctx.offs, ctx.sizes_cpu = cumsums, offs, sizes_cpu
@@ -411,6 +420,7 @@ class _PeerEpMlp(torch.autograd.Function):
         rows = cumsums[-1]
         dev = dy.device
         wgrad, dgrad = ctx.need_wgrad, ctx.need_dgrad
+        need_t = wgrad and ctx.need_t
         ms = metas.get_meta_strided
 
         recv_ptrs = ectx.recv.ptrs
@@ -439,10 +449,10 @@ class _PeerEpMlp(torch.autograd.Function):
         else:
             recv = ectx.recv.tensor((rows, hidden), torch.bfloat16)
             grad_out_fp8 = torch.empty(rows, hidden, dtype=gdt, device=dev)
-        grad_out_t = torch.empty(offs[-1], hidden, dtype=gdt, device=dev) if wgrad else None
-        act_t = torch.empty(offs[-1], ffn, dtype=act_fp8.dtype, device=dev) if wgrad else None
+        grad_out_t = torch.empty(offs[-1], hidden, dtype=gdt, device=dev) if need_t else None
+        act_t = torch.empty(offs[-1], ffn, dtype=act_fp8.dtype, device=dev) if need_t else None
         grad_pre_fp8 = torch.empty(rows, fc1_out, dtype=gdt, device=dev)
-        grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=gdt, device=dev) if wgrad else None
+        grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=gdt, device=dev) if need_t else None
         grad_fc1 = torch.empty(ctx.fc1_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
         grad_fc2 = torch.empty(ctx.fc2_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
         gi_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev) if dgrad else None
@@ -456,7 +466,7 @@ class _PeerEpMlp(torch.autograd.Function):
             r0, r1 = cumsums[j0], cumsums[j1]
             t0, t1 = offs[j0], offs[j1]
             live = r1 > r0
-            if live and wgrad:
+            if live and need_t:
                 # needs no gradient rows: runs while they are still on their way
                 backend.grouped_cast_transpose(act_fp8[r0:r1], _rel(cumsums, j0, j1), None, act_t[t0:t1], _rel(offs, j0, j1),
                                                None, None)
@@ -466,19 +476,22 @@ class _PeerEpMlp(torch.autograd.Function):
             if live:
                 if not fp8d:
                     backend.grouped_cast_transpose(
-                        recv[r0:r1], _rel(cumsums, j0, j1), grad_out_fp8[r0:r1], grad_out_t[t0:t1] if wgrad else None,
+                        recv[r0:r1], _rel(cumsums, j0, j1), grad_out_fp8[r0:r1], grad_out_t[t0:t1] if need_t else None,
                         _rel(offs, j0, j1), ms(_T.kGradOutputGroup1, _M.kScale, j0), ms(_T.kGradOutputGroup1, _M.kAmax, j0))
-                elif wgrad:
+                elif need_t:
                     backend.grouped_cast_transpose(grad_out_fp8[r0:r1], _rel(cumsums, j0, j1), None, grad_out_t[t0:t1],
                                                    _rel(offs, j0, j1), None, None)
                 dy_si = ms(_T.kGradOutputGroup1, _M.kScaleInv, j0)
-                if wgrad:
+                if need_t:
                     backend.grouped_wgrad(grad_out_t[t0:t1], act_t[t0:t1], _rel(offs, j0, j1), hidden, ffn, dy_si,
                                           ms(_T.kForwardInputGroup2, _M.kScaleInv, j0), c=grad_fc2[j0:j1])
+                elif wgrad:
+                    backend.grouped_wgrad_rowmajor(grad_out_fp8[r0:r1], act_fp8[r0:r1], _rel(cumsums, j0, j1), dy_si,
+                                                   ms(_T.kForwardInputGroup2, _M.kScaleInv, j0), c=grad_fc2[j0:j1])
                 grad_act = backend.fp8_gmm(grad_out_fp8[r0:r1], fc2_w_t[j0:j1], sizes_cpu[j0:j1], dy_si,
                                            ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), backward=True)
                 backend.grouped_cast_transpose(
-                    grad_act, _rel(cumsums, j0, j1), grad_pre_fp8[r0:r1], grad_pre_t[t0:t1] if wgrad else None,
+                    grad_act, _rel(cumsums, j0, j1), grad_pre_fp8[r0:r1], grad_pre_t[t0:t1] if need_t else None,
                     _rel(offs, j0, j1), ms(_T.kGradOutputGroup2, _M.kScale, j0), ms(_T.kGradOutputGroup2, _M.kAmax, j0),
                     in2=pre_act[r0:r1], activation=activation)
                 dpre_si = ms(_T.kGradOutputGroup2, _M.kScaleInv, j0)
@@ -494,9 +507,13 @@ class _PeerEpMlp(torch.autograd.Function):
                                      for s, d, l, n in plan.combine_blocks((j0, j1))])
             else:
                 last = ch_back.push([])
-            if live and wgrad:
+            if live and need_t:
                 backend.grouped_wgrad(grad_pre_t[t0:t1], input_t_fp8[t0:t1], _rel(offs, j0, j1), fc1_out, hidden, dpre_si,
                                       ms(_T.kForwardInputGroup1, _M.kScaleInv, j0), c=grad_fc1[j0:j1])
+            elif live and wgrad:
+                # `input_t_fp8` holds the row-major FP8 input here
+                backend.grouped_wgrad_rowmajor(grad_pre_fp8[r0:r1], input_t_fp8[r0:r1], _rel(cumsums, j0, j1), dpre_si,
+                                               ms(_T.kForwardInputGroup1, _M.kScaleInv, j0), c=grad_fc1[j0:j1])
         ch_back.wait(last)
         return gi, grad_fc1, grad_fc2, None
 

@@ -7,7 +7,9 @@ saved-tensor layout, meta slots), re-implemented on this package's kernels:
   per-group views, so host time does not grow with the number of groups;
 * the forward / dgrad GEMM is one launch with the de-scale fused (the reference's CUTLASS path needs a
   second pass, fp8_gmm/backend.py:78-82);
-* the weight gradient is one grouped launch (the reference loops over groups, :165-182);
+* the weight gradient is one grouped launch (the reference loops over groups, :165-182) that reads the row-major FP8
+  activations directly (MN-major tensor-core operands), so the padded transposes the reference builds for it
+  (:32-52,:133-149) are not made; FP8GMM_WGRAD=transposed restores that dataflow;
 * ``is_first_microbatch`` works (the reference forces None): True casts the weights and keeps the FP8 copies, False
   reuses them and leaves the scales alone, so gradient accumulation pays the weight cast once per optimizer step;
 * groups with zero rows are accepted (the reference asserts, :205): they produce no output rows and a
@@ -29,7 +31,8 @@ class _GroupedLinear(torch.autograd.Function):
     def forward(ctx, input, weight, group_sizes, fp8_meta, is_grad_enabled, cutlass, weight_cache=None, reuse_weights=False):
         need_wgrad = is_grad_enabled and weight.requires_grad
         need_dgrad = is_grad_enabled and input.requires_grad
-        num_groups, padded, cumsums, padded_cumsums = cumsum_group_sizes(group_sizes.tolist(), need_padding=need_wgrad)
+        need_t = need_wgrad and not backend.WGRAD_ROWMAJOR   # padded transposes only for the reference's wgrad dataflow
+        num_groups, padded, cumsums, padded_cumsums = cumsum_group_sizes(group_sizes.tolist(), need_padding=need_t)
         offs = padded_cumsums if padded else cumsums
         metas = Fp8MetaWrapper(num_groups, fp8_meta)
         dtype = get_fp8_te_dtype(fp8_meta["recipe"], fprop_tensor=True)
@@ -39,7 +42,7 @@ class _GroupedLinear(torch.autograd.Function):
         input = input.contiguous()
 
         input_fp8 = torch.empty(input.shape, dtype=torch_dtype, device=input.device)
-        input_t_fp8 = torch.empty(offs[-1], k, dtype=torch_dtype, device=input.device) if need_wgrad else None
+        input_t_fp8 = torch.empty(offs[-1], k, dtype=torch_dtype, device=input.device) if need_t else None
         backend.grouped_cast_transpose(
             input, cumsums, input_fp8, input_t_fp8, offs,
             metas.get_meta_strided(_T.kInputGroup1, _M.kScale), metas.get_meta_strided(_T.kInputGroup1, _M.kAmax))
@@ -51,7 +54,8 @@ class _GroupedLinear(torch.autograd.Function):
             metas.get_meta_strided(_T.kInputGroup1, _M.kScaleInv), metas.get_meta_strided(_T.kWeightGroup1, _M.kScaleInv),
             backward=False, cutlass=cutlass)
         if is_grad_enabled:
-            ctx.save_for_backward(input_t_fp8, weight_t_fp8, group_sizes)
+            ctx.save_for_backward(input_t_fp8 if need_t else (input_fp8 if need_wgrad else None), weight_t_fp8, group_sizes)
+            ctx.need_t = need_t
             ctx.num_groups = num_groups
             metas.set_forward_scale_inv_cloned()
             ctx.fp8_meta_wrapper = metas
@@ -73,7 +77,7 @@ class _GroupedLinear(torch.autograd.Function):
         _, n, k = ctx.weight_shape
         grad_out_fp8 = torch.empty(grad_out.shape, dtype=g_dtype, device=grad_out.device)
         grad_out_t_fp8 = (torch.empty(offs[-1], n, dtype=g_dtype, device=grad_out.device)
-                          if ctx.weight_requires_grad else None)
+                          if ctx.weight_requires_grad and ctx.need_t else None)
         backend.grouped_cast_transpose(
             grad_out, cumsums, grad_out_fp8, grad_out_t_fp8, offs,
             metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScale), metas.get_meta_strided(_T.kGradOutputGroup1, _M.kAmax))
@@ -85,9 +89,15 @@ class _GroupedLinear(torch.autograd.Function):
                 metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv),
                 backward=True, cutlass=ctx.cutlass)
         grad_weight = None
-        if ctx.weight_requires_grad:
+        if ctx.weight_requires_grad and ctx.need_t:
             grad_weight = backend.grouped_wgrad(
                 grad_out_t_fp8, input_t_fp8, offs, n, k,
+                metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScaleInv),
+                metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
+        elif ctx.weight_requires_grad:
+            # `input_t_fp8` holds the row-major FP8 input here: the GEMM reads both operands as they lie
+            grad_weight = backend.grouped_wgrad_rowmajor(
+                grad_out_fp8, input_t_fp8, cumsums,
                 metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScaleInv),
                 metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
         return grad_input, grad_weight, None, None, None, None, None, None

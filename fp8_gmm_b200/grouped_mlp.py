@@ -28,7 +28,8 @@ class _GroupedMlp(torch.autograd.Function):
         weight_requires_grad = fc1_weight.requires_grad
         need_wgrad = is_grad_enabled and weight_requires_grad
         need_dgrad = is_grad_enabled and input_requires_grad
-        num_groups, padded, cumsums, padded_cumsums = cumsum_group_sizes(group_sizes.tolist(), need_padding=need_wgrad)
+        need_t = need_wgrad and not backend.WGRAD_ROWMAJOR   # padded transposes only for the reference's wgrad dataflow
+        num_groups, padded, cumsums, padded_cumsums = cumsum_group_sizes(group_sizes.tolist(), need_padding=need_t)
         offs = padded_cumsums if padded else cumsums
         metas = Fp8MetaWrapper(num_groups, fp8_meta)
         torch_dtype = to_torch_dtype(get_fp8_te_dtype(fp8_meta["recipe"], fprop_tensor=True))
@@ -40,14 +41,14 @@ class _GroupedMlp(torch.autograd.Function):
         input = input.contiguous()
 
         input_fp8 = torch.empty(input.shape, dtype=torch_dtype, device=input.device)
-        input_t_fp8 = torch.empty(offs[-1], hidden, dtype=torch_dtype, device=input.device) if need_wgrad else None
+        input_t_fp8 = torch.empty(offs[-1], hidden, dtype=torch_dtype, device=input.device) if need_t else None
         x_scale, x_amax = metas.get_meta_strided(_T.kInputGroup1, _M.kScale), metas.get_meta_strided(_T.kInputGroup1, _M.kAmax)
         if perm is None:
             backend.grouped_cast_transpose(input, cumsums, input_fp8, input_t_fp8, offs, x_scale, x_amax)
         else:
             # rows arrive in an external (source-major) order: the cast itself puts them expert-major
             backend.blocked_cast(input, input_fp8, perm, x_scale, x_amax, num_groups)
-            if need_wgrad:
+            if need_t:
                 backend.grouped_cast_transpose(input_fp8, cumsums, None, input_t_fp8, offs, None, None)
         fc1_w_fp8, fc1_w_t = cast_weight_cached(
             fc1_weight, torch_dtype, need_dgrad,
@@ -73,7 +74,9 @@ class _GroupedMlp(torch.autograd.Function):
             metas.get_meta_strided(_T.kInputGroup2, _M.kScaleInv), metas.get_meta_strided(_T.kWeightGroup2, _M.kScaleInv),
             backward=False, c_row_map=None if perm is None else perm.row_map)
         if is_grad_enabled:
-            ctx.save_for_backward(input_t_fp8, fc1_w_t, fc2_w_t, pre_act, act_fp8 if need_wgrad else None, group_sizes)
+            ctx.save_for_backward(input_t_fp8 if need_t else (input_fp8 if need_wgrad else None), fc1_w_t, fc2_w_t, pre_act,
+                                  act_fp8 if need_wgrad else None, group_sizes)
+            ctx.need_t = need_t
             ctx.num_groups = num_groups
             metas.set_forward_scale_inv_cloned()
             ctx.fp8_meta_wrapper = metas
@@ -100,32 +103,36 @@ class _GroupedMlp(torch.autograd.Function):
         ffn = ctx.fc2_weight_shape[2]
         dev = grad_out.device
         wgrad = ctx.weight_requires_grad
+        need_t = wgrad and ctx.need_t
 
         perm = ctx.perm
         grad_out_fp8 = torch.empty(grad_out.shape, dtype=g_dtype, device=dev)
-        grad_out_t = torch.empty(offs[-1], hidden, dtype=g_dtype, device=dev) if wgrad else None
+        grad_out_t = torch.empty(offs[-1], hidden, dtype=g_dtype, device=dev) if need_t else None
         dy_scale, dy_amax = (metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScale),
                              metas.get_meta_strided(_T.kGradOutputGroup1, _M.kAmax))
         if perm is None:
             backend.grouped_cast_transpose(grad_out, cumsums, grad_out_fp8, grad_out_t, offs, dy_scale, dy_amax)
         else:
             backend.blocked_cast(grad_out, grad_out_fp8, perm, dy_scale, dy_amax, ctx.num_groups)
-            if wgrad:
+            if need_t:
                 backend.grouped_cast_transpose(grad_out_fp8, cumsums, None, grad_out_t, offs, None, None)
         dy_scale_inv = metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScaleInv)
         grad_fc2_weight = None
-        if wgrad:
+        if need_t:
             act_t = torch.empty(offs[-1], ffn, dtype=act_fp8.dtype, device=dev)
             backend.grouped_cast_transpose(act_fp8, cumsums, None, act_t, offs, None, None)
             grad_fc2_weight = backend.grouped_wgrad(
                 grad_out_t, act_t, offs, hidden, ffn, dy_scale_inv,
                 metas.get_meta_strided(_T.kForwardInputGroup2, _M.kScaleInv))
+        elif wgrad:
+            grad_fc2_weight = backend.grouped_wgrad_rowmajor(
+                grad_out_fp8, act_fp8, cumsums, dy_scale_inv, metas.get_meta_strided(_T.kForwardInputGroup2, _M.kScaleInv))
         grad_act = backend.fp8_gmm(
             grad_out_fp8, fc2_w_t, group_sizes, dy_scale_inv,
             metas.get_meta_strided(_T.kForwardWeightGroup2, _M.kScaleInv), backward=True)
         # d(activation) fused with the e5m2 cast, the padded transpose and the amax
         grad_pre_fp8 = torch.empty(pre_act.shape, dtype=g_dtype, device=dev)
-        grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=g_dtype, device=dev) if wgrad else None
+        grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=g_dtype, device=dev) if need_t else None
         backend.grouped_cast_transpose(
             grad_act, cumsums, grad_pre_fp8, grad_pre_t, offs,
             metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScale), metas.get_meta_strided(_T.kGradOutputGroup2, _M.kAmax),
@@ -141,10 +148,14 @@ class _GroupedMlp(torch.autograd.Function):
                 handle = torch.distributed.all_reduce(
                     grad_input, op=torch.distributed.ReduceOp.SUM, group=ctx.tp_group, async_op=True)
         grad_fc1_weight = None
-        if wgrad:
+        if need_t:
             grad_fc1_weight = backend.grouped_wgrad(
                 grad_pre_t, input_t_fp8, offs, fc1_out, hidden, dpre_scale_inv,
                 metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
+        elif wgrad:
+            # `input_t_fp8` holds the row-major FP8 input here
+            grad_fc1_weight = backend.grouped_wgrad_rowmajor(
+                grad_pre_fp8, input_t_fp8, cumsums, dpre_scale_inv, metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
         if handle is not None:
             handle.wait()
         return grad_input, grad_fc1_weight, grad_fc2_weight, None, None, None, None, None, None, None, None, None

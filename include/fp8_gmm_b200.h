@@ -288,6 +288,17 @@ int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* args, void* stream);
 int fp8gmm_set_gemm_sm_limit(int sms);
 
 /*
+ * Weight gradients without the padded-transposed operands: a_t / b_t of fp8gmm_wgrad_args are here the ROW-MAJOR fp8
+ * activations, a_t = dY (sum m x n) and b_t = X (sum m x k), and t_offsets the plain row prefix sums of the groups
+ * (any sizes, zero allowed; no rounding to 16).  C_g (n x k) = (dY_g * sa[g])^T (X_g * sb[g]); the tensor cores read
+ * both operands MN-major, rows past a group's end are zero-filled by TMA.  Same result as fp8gmm_grouped_wgrad on
+ * the padded transposes of the same rows (reference fp8_gmm/grouped_linear.py:165-182), without the transposes the
+ * reference builds solely for this GEMM (fp8_gmm/grouped_linear.py:32-52,133-149).  Workspace as for
+ * fp8gmm_grouped_wgrad.
+ */
+int fp8gmm_grouped_wgrad_rowmajor(const fp8gmm_wgrad_args* args, void* stream);
+
+/*
  * Profiling aid with no counterpart in the reference: while a device buffer of at least
  * 8 * sizeof(int64) * (number of CTAs launched, at most 148) bytes is installed, every grouped-GEMM CTA
  * writes its stall counters in SM clock cycles to buffer[cta*8 + i]:

@@ -19,3 +19,15 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(params=["rowmajor", "transposed"])
+def wgrad_dataflow(request):
+    """Runs a module test under both weight-gradient dataflows: operands read row-major by the GEMM (default) and the
+    reference's padded transposes (FP8GMM_WGRAD=transposed)."""
+    from fp8_gmm_b200 import backend
+
+    saved = backend.WGRAD_ROWMAJOR
+    backend.WGRAD_ROWMAJOR = request.param == "rowmajor"
+    yield request.param
+    backend.WGRAD_ROWMAJOR = saved

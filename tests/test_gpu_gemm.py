@@ -133,6 +133,37 @@ def test_grouped_wgrad_matches_oracle(cuda, sizes, n, k):
             assert (c[g] == 0).all()
 
 
+@pytest.mark.parametrize("sizes,n,k", [([128, 96, 160, 128], 1024, 512), ([5, 0, 33, 130, 257], 256, 512), ([16, 32, 16], 64, 32),
+                                       ([700, 1], 384, 272), ([0, 0], 256, 256)])
+def test_rowmajor_wgrad_equals_the_transposed_path(cuda, sizes, n, k):
+    """fp8gmm_grouped_wgrad_rowmajor reads dY and X as they lie (MN-major operands); it must give what the
+    padded-transposed path gives on the same rows, and match the oracle."""
+    from fp8_gmm_b200 import backend
+    from fp8_gmm_b200.utils import cumsum_group_sizes
+
+    G, padded, cums, pcs = cumsum_group_sizes(sizes, need_padding=True)
+    offs = pcs if padded else cums
+    dy, x = randn_bf16((cums[-1], n), n + 1), randn_bf16((cums[-1], k), k + 1)
+    dy_q, x_q = O.quantize(dy, 3.0, E5), O.quantize(x, 5.0, E4)
+    dy_t = [O.pad_transpose(dy_q[cums[g]:cums[g + 1]], offs[g + 1] - offs[g]) for g in range(G)]
+    x_t = [O.pad_transpose(x_q[cums[g]:cums[g + 1]], offs[g + 1] - offs[g]) for g in range(G)]
+    sa, sb = torch.linspace(0.2, 0.4, G), torch.linspace(0.1, 0.3, G)
+    c = torch.full((G, n, k), float("nan"), dtype=torch.bfloat16, device=cuda)
+    backend.grouped_wgrad_rowmajor(dy_q.to(cuda), x_q.to(cuda), cums, sa.to(cuda), sb.to(cuda), c=c)
+    backend.device_status()
+    assert not torch.isnan(c.float()).any()
+    ref = O.grouped_wgrad(dy_t, x_t, sa, sb)
+    assert O.rel_frobenius(c.cpu(), ref) <= 4e-3
+    if cums[-1] > 0:
+        a_t = torch.cat([u8(t).reshape(-1) for t in dy_t]).view(E5).to(cuda)
+        b_t = torch.cat([u8(t).reshape(-1) for t in x_t]).view(E4).to(cuda)
+        c2 = backend.grouped_wgrad(a_t, b_t, offs, n, k, sa.to(cuda), sb.to(cuda))
+        assert torch.equal(c, c2), "same products, same accumulation order: the two paths must agree bit for bit"
+    for g, s in enumerate(sizes):
+        if s == 0:
+            assert (c[g] == 0).all()
+
+
 def test_mixtral_shaped_slice_properties(cuda):
     """Full-size shapes (BASELINE config 2: hidden 4096, ffn 14336) on a slice the oracle cannot afford:
     checked through size-independent properties -- linearity in the per-group scales and agreement of a

@@ -23,7 +23,7 @@ def _first_step_scales(G, n_fwd=3, n_bwd=2):
 
 
 @pytest.mark.parametrize("sizes,k,n", [([128, 96, 160, 128], 512, 1024), ([5, 0, 33, 130], 64, 48)])
-def test_grouped_linear_first_step_matches_oracle(cuda, sizes, k, n):
+def test_grouped_linear_first_step_matches_oracle(cuda, wgrad_dataflow, sizes, k, n):
     import fp8_gmm_b200 as fg
 
     G, m = len(sizes), sum(sizes)
@@ -99,7 +99,7 @@ def _mlp_oracle_scales(G):
 
 @pytest.mark.parametrize("act", ["gelu", "swiglu"])
 @pytest.mark.parametrize("sizes,h,f", [([128, 96, 160, 128], 256, 512), ([5, 0, 33, 130], 64, 96)])
-def test_grouped_mlp_first_step_matches_oracle(cuda, act, sizes, h, f):
+def test_grouped_mlp_first_step_matches_oracle(cuda, wgrad_dataflow, act, sizes, h, f):
     import fp8_gmm_b200 as fg
 
     G, m = len(sizes), sum(sizes)
