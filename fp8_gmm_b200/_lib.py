@@ -47,7 +47,7 @@ class GemmArgs(ctypes.Structure):
         ("activation", ctypes.c_int), ("act_out", c_vp),
         ("act_scale", c_fp), ("act_scale_stride", c_i64),
         ("act_amax", c_fp), ("act_amax_stride", c_i64),
-        ("c_row_map", c_vp),
+        ("c_row_map", c_vp), ("b_layout", ctypes.c_int),
     ]
 
 

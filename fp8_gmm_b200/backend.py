@@ -23,6 +23,10 @@ _FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
 # padded-transposed copies.  FP8GMM_WGRAD=transposed selects the reference's dataflow instead (padded transposes
 # written by the cast kernels, reference fp8_gmm/grouped_linear.py:32-52,133-149, consumed by grouped_wgrad).
 WGRAD_ROWMAJOR = os.environ.get("FP8GMM_WGRAD", "rowmajor") != "transposed"
+# Data gradients multiply by the forward FP8 weights (G, out, in) as they are (fp8_gmm(..., b_is_kn=True)), so the
+# modules make no per-expert weight transposes either.  FP8GMM_DGRAD=transposed selects the reference's dataflow
+# (weights cast into (G, in, out) transposes, reference fp8_gmm/grouped_linear.py:70-73).
+DGRAD_KN = os.environ.get("FP8GMM_DGRAD", "kn") != "transposed"
 ACT_NONE, ACT_GELU, ACT_SWIGLU = 0, 1, 2
 _ACT_CODE = {None: 0, "none": 0, "gelu": 1, "swiglu": 2}
 
@@ -332,13 +336,14 @@ def blocked_cast(inp, out, perm, scale, amax, num_groups):
         a.scatter()
 
 
-def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None):
+def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None, b_layout=0):
     args = GemmArgs()
     args.a, args.b, args.c = a.data_ptr(), b3.data_ptr(), c.data_ptr()
     ms, keep = _i64_array(m_sizes)
     args.m_sizes = ms
     args.num_groups = num_groups
-    args.n, args.k = b3.shape[-2], b3.shape[-1]
+    args.n, args.k = (b3.shape[-2], b3.shape[-1]) if b_layout == 0 else (b3.shape[-1], b3.shape[-2])
+    args.b_layout = b_layout
     args.a_format, args.b_format = _fp8_code(a.dtype), _fp8_code(b3.dtype)
     args.a_scale_inv, args.a_scale_inv_stride = sa.ptr, sa.stride
     args.b_scale_inv, args.b_scale_inv_stride = sb.ptr, sb.stride
@@ -401,6 +406,7 @@ def fp8_gmm(
     cutlass=False,
     activation="gelu",
     c_row_map=None,
+    b_is_kn=False,
 ):
     """Grouped GEMM ``c[rows of g] = (a[rows of g] * sa[g]) (b[g] * sb[g])^T`` in one launch.
 
@@ -413,14 +419,16 @@ def fp8_gmm(
     activation scaled by c_scales[g], c_amaxes[g] the amax.  activation="swiglu" expects b = [gate
     rows | up rows] (N = 2F) and produces a (sum m, F) ``c``.  ``c_row_map`` (CUDA int32, one entry per row
     of a; plain bf16 output only) makes the epilogue store row r of the product at row c_row_map[r] of c.
+    ``b_is_kn=True``: b is (G, K, N) row-major and ``c = a @ b[g]`` without a transpose -- dgrad with the forward weights
+    (G, out, in) as they are (the tensor cores read B MN-major; no per-expert weight transposes needed).
     """
     _cuda_2d(a, "a", _FP8)
     _cuda_2d(b, "b", _FP8)
     _require(a.dim() == 2 and b.dim() == 3, "fp8_gmm: a must be 2-D and b 3-D")
-    _require(a.shape[1] == b.shape[2], "fp8_gmm: contraction dimensions differ")
+    _require(a.shape[1] == (b.shape[1] if b_is_kn else b.shape[2]), "fp8_gmm: contraction dimensions differ")
     G = b.shape[0]
     _require(len(group_sizes) == G, "fp8_gmm: one group size per expert is required")
-    n_out = b.shape[1]
+    n_out = b.shape[2] if b_is_kn else b.shape[1]
     fused = (c is not None and c.dtype in _FP8) or (c is None and c_dtype in _FP8)
     if fused and activation == "swiglu":
         n_out = b.shape[1] // 2
@@ -431,6 +439,7 @@ def fp8_gmm(
         _require(c.dtype == torch.bfloat16 and pre_gelu_out is None, "fp8_gmm: cutlass=True has no fused activation")
     sa = _strided(a_scale_invs, G)
     sb = _strided(b_scale_invs, G)
+    _require(not (fused and b_is_kn), "fp8_gmm: b_is_kn has no fused activation")
     if fused:
         _require(c.dtype == torch.float8_e4m3fn, "fp8_gmm: FP8 output must be e4m3")
         _require(c_scales is not None and c_amaxes is not None, "fp8_gmm: FP8 output needs c_scales and c_amaxes")
@@ -441,7 +450,8 @@ def fp8_gmm(
     else:
         _require(c.dtype == torch.bfloat16, "fp8_gmm: output must be bfloat16 or float8_e4m3fn")
         _require(pre_gelu_out is None, "fp8_gmm: pre_gelu_out needs an FP8 output")
-        _gemm(a, b, c, group_sizes, G, sa, sb, ACT_NONE, None, _Strided(None, 0), _Strided(None, 0), c_row_map)
+        _gemm(a, b, c, group_sizes, G, sa, sb, ACT_NONE, None, _Strided(None, 0), _Strided(None, 0), c_row_map,
+              b_layout=1 if b_is_kn else 0)
     return c
 
 

@@ -79,6 +79,7 @@ struct GemmParams {
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
   int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
+  int b_mn;            // kModeRows only: B is (G, K, N) row-major, read MN-major through the 3-D map_b (x = n, y = k, z = group)
   int mn_major;        // kModeWgrad only: operands are row-major (rows x features) slices, i.e. MN-major for the MMA
   int super_tiles;     // m-tiles per super-row of the tile order (see decode_tile)
   int tma_store;       // 1: full 32-row slabs of a tile leave through shared memory + TMA stores (map_c is valid)
@@ -150,6 +151,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
@@ -325,6 +332,12 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -471,14 +484,23 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             if (kCtas == 1) {
               mbar_expect_tx(full_bar(stage), kStageBytes);
               tma_load_2d(sa, map_a, full_bar(stage), mn ? ya : kx, mn ? kx : ya);
-              tma_load_2d(sb, map_b, full_bar(stage), mn ? yb0 : kx, mn ? kx : yb0);
-              tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), mn ? yb1 : kx, mn ? kx : yb1);
+              if (p.b_mn) {
+                // B = (G, K, N): x = output column inside the group, y = contraction row, z = group
+                tma_load_3d(sb, map_b, full_bar(stage), yb0 - b_base, kx, t.group);
+                tma_load_3d(sb + kTileBBytes / 2, map_b, full_bar(stage), yb1 - b_base, kx, t.group);
+              } else {
+                tma_load_2d(sb, map_b, full_bar(stage), mn ? yb0 : kx, mn ? kx : yb0);
+                tma_load_2d(sb + kTileBBytes / 2, map_b, full_bar(stage), mn ? yb1 : kx, mn ? kx : yb1);
+              }
             } else {
               // both CTAs credit the leader's barrier; the leader arms it for the bytes of both
               const uint32_t bar = full0_leader + 8u * stage;
               if (leader) mbar_expect_tx(full_bar(stage), 2 * kStageBytes);
               tma_load_2d_pair(sa, map_a, bar, mn ? ya : kx, mn ? kx : ya);
-              tma_load_2d_pair(sb, map_b, bar, mn ? yb_mine : kx, mn ? kx : yb_mine);
+              if (p.b_mn)
+                tma_load_3d_pair(sb, map_b, bar, yb_mine - b_base, kx, t.group);
+              else
+                tma_load_2d_pair(sb, map_b, bar, mn ? yb_mine : kx, mn ? kx : yb_mine);
             }
           }
           if (++stage == kStages) {
@@ -503,11 +525,12 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       long long wait_full = 0, wait_tempty = 0, issue = 0;
       const long long t_begin = p.profile ? clock64() : 0;
       const unsigned long long ns_begin = p.profile ? global_ns() : 0;
-      const bool mn = p.mn_major != 0;
-      const uint64_t desc_a0 = mn ? make_smem_desc_mn(tiles_addr, 16) : make_smem_desc(tiles_addr);
-      const uint64_t desc_b0 = mn ? make_smem_desc_mn(tiles_addr + kTileABytes, kTileBBytes / 2) : make_smem_desc(tiles_addr + kTileABytes);
+      const bool a_mn = p.mn_major != 0, b_mn = p.mn_major != 0 || p.b_mn != 0;
+      const uint64_t desc_a0 = a_mn ? make_smem_desc_mn(tiles_addr, 16) : make_smem_desc(tiles_addr);
+      const uint64_t desc_b0 = b_mn ? make_smem_desc_mn(tiles_addr + kTileABytes, kTileBBytes / 2) : make_smem_desc(tiles_addr + kTileABytes);
       // one MMA consumes 32 contraction bytes: 32 bytes along a K-major row, or 32 rows of 128 bytes (MN-major)
-      const uint64_t k_step = mn ? (32ull * 128ull) >> 4 : 32ull >> 4;
+      const uint64_t a_step = a_mn ? (32ull * 128ull) >> 4 : 32ull >> 4;
+      const uint64_t b_step = b_mn ? (32ull * 128ull) >> 4 : 32ull >> 4;
       const uint32_t idesc = p.idesc;
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
         const TileInfo t = decode_tile<kCtas>(p, tile, rank);
@@ -528,11 +551,11 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
           const uint64_t db = desc_b0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
 #pragma unroll
           for (int k = 0; k < kBlockK / 32; ++k) {
-            // advance both descriptors by one MMA's worth of contraction (k_step is in 16-byte units)
+            // advance both descriptors by one MMA's worth of contraction (the steps are in 16-byte units)
             if (kCtas == 1)
-              umma_f8(tmem_d, da + k_step * k, db + k_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_f8(tmem_d, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
             else
-              umma_f8_pair(tmem_d, da + k_step * k, db + k_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_f8_pair(tmem_d, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           if (kCtas == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage));
           if (p.profile) {
@@ -850,6 +873,30 @@ int encode_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols)
   return FP8GMM_OK;
 }
 
+// 3-D uint8 tensor (groups x rows x cols bytes), box 1 x 128 rows x 128 bytes, SWIZZLE_128B: the (G, K, N) weights
+// read MN-major.  Rows past a group's end are zero-filled (they are out of bounds of the middle dimension), so a
+// contraction that is not a multiple of 128 never reads the next group's rows.
+int encode_map_3d(CUtensorMap* map, const void* base, uint64_t groups, uint64_t rows, uint64_t cols) {
+  auto fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return FP8GMM_CUDA_ERROR;
+  }
+  const cuuint64_t dims[3] = {cols, rows, groups};
+  const cuuint64_t strides[2] = {cols, rows * cols};
+  const cuuint32_t box[3] = {kBlockK, 128, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (3-D) failed with %d (base %p, %llu x %llu x %llu)", static_cast<int>(r), base,
+              static_cast<unsigned long long>(groups), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols));
+    return FP8GMM_CUDA_ERROR;
+  }
+  return FP8GMM_OK;
+}
+
 // 2-D bf16 tensor (rows x cols, row pitch = cols) for the epilogue's TMA stores: box 32 rows x 64 columns
 // (128 bytes per row), SWIZZLE_128B to match the staging layout.
 int encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
@@ -880,7 +927,7 @@ bool tma_epilogue_enabled() {
   return !(e != nullptr && e[0] == 'd');
 }
 
-uint32_t make_idesc(int a_format, int b_format, int ctas, bool mn_major = false) {
+uint32_t make_idesc(int a_format, int b_format, int ctas, bool a_mn = false, bool b_mn = false) {
   // tcgen05 instruction descriptor, kind::f8f6f4: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format
   // (0 = e4m3, 1 = e5m2), bits 15/16 = A / B major (0 = K-major, 1 = MN-major), [17,23) N >> 3, [24,29) M >> 4.
   uint32_t d = 0;
@@ -889,7 +936,8 @@ uint32_t make_idesc(int a_format, int b_format, int ctas, bool mn_major = false)
   d |= static_cast<uint32_t>(b_format) << 10;
   d |= static_cast<uint32_t>(kBlockN >> 3) << 17;
   d |= static_cast<uint32_t>((kBlockM * ctas) >> 4) << 24;  // a CTA pair issues M = 256
-  if (mn_major) d |= (1u << 15) | (1u << 16);               // A and B are MN-major ("transposed") in shared memory
+  if (a_mn) d |= 1u << 15;  // A is MN-major ("transposed") in shared memory
+  if (b_mn) d |= 1u << 16;  // B is MN-major
   return d;
 }
 
@@ -912,7 +960,7 @@ int launch(GemmParams& p, int ctas, cudaStream_t s) {
   if (g_sm_limit > 0 && g_sm_limit < sms) sms = g_sm_limit;
   const int workers = sms / ctas > 0 ? sms / ctas : 1;
   const int grid = ctas * (p.total_tiles < workers ? p.total_tiles : workers);
-  p.prefetch_kb = prefetch_distance();
+  p.prefetch_kb = p.b_mn ? 0 : prefetch_distance();  // the experimental prefetch only knows the 2-D operand maps
   p.profile = (g_profile != nullptr && g_profile_bytes >= static_cast<size_t>(grid) * 8 * sizeof(long long)) ? g_profile : nullptr;
   if (ctas == 2) {
     FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
@@ -992,8 +1040,14 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   FP8GMM_CHECK_ARG(static_cast<int64_t>(a->num_groups) * a->n <= INT32_MAX - 1024, "grouped_gemm: G*N too large");
   int rc = encode_map(&p.map_a, a->a, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->k));
   if (rc != FP8GMM_OK) return rc;
-  rc = encode_map(&p.map_b, a->b, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
+  FP8GMM_CHECK_ARG(a->b_layout == 0 || a->b_layout == 1, "grouped_gemm: bad b_layout %d", a->b_layout);
+  FP8GMM_CHECK_ARG(a->b_layout == 0 || a->activation == FP8GMM_ACT_NONE, "grouped_gemm: b_layout 1 has no fused activation");
+  if (a->b_layout == 1)
+    rc = encode_map_3d(&p.map_b, a->b, static_cast<uint64_t>(a->num_groups), static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->n));
+  else
+    rc = encode_map(&p.map_b, a->b, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
   if (rc != FP8GMM_OK) return rc;
+  p.b_mn = a->b_layout;
   p.maps = nullptr;
   p.c = static_cast<uint16_t*>(a->c);
   p.act_out = static_cast<uint8_t*>(a->act_out);
@@ -1020,7 +1074,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.k = static_cast<int>(a->k);
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = static_cast<int>(tiles);
-  p.idesc = make_idesc(a->a_format, a->b_format, ctas);
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas, false, a->b_layout == 1);
   p.super_tiles = (a->k > kLongK ? kSuperRowsLongK : kSuperRowsShortK) / tile_m;
   if (a->c_row_map == nullptr && a->activation != FP8GMM_ACT_GELU && tma_epilogue_enabled()) {
     rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
@@ -1193,7 +1247,7 @@ int fp8gmm_grouped_wgrad_rowmajor(const fp8gmm_wgrad_args* a, void* stream) {
   p.k = 0;
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
-  p.idesc = make_idesc(a->a_format, a->b_format, ctas, true);
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas, true, true);
   p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
   if (tma_epilogue_enabled()) {
     const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));

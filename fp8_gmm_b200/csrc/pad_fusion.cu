@@ -577,6 +577,9 @@ int fp8gmm_grouped_pad_cast_transpose(const fp8gmm_grouped_cast_args* a, void* s
     t.scale = a->scale ? a->scale + g * a->scale_stride : nullptr;
     t.amax = a->amax ? a->amax + g * a->amax_stride : nullptr;
   }
+  // without a transposed output the plain cast is the flat quantise kernel's job (same bytes, same amax, no
+  // shared-memory staging)
+  if (mode == kCast && a->out_t == nullptr) return fp8gmm_multi_quantize(descs.data(), a->num_groups, a->out_format, stream);
   return run(descs.data(), a->num_groups, mode, a->out_format, stream, "grouped_pad_cast_transpose");
 }
 

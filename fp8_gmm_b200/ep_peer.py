@@ -340,7 +340,8 @@ class _PeerEpMlp(torch.autograd.Function):
         # the fc2 weight cast runs while the first rows are on their way
         cache, reuse = st["weight_cache"], st["reuse_weights"]
         fc1_w_fp8, fc1_w_t = st["fc1_fp8"]   # cast before the size exchange, so the GPU had work during the host sync
-        fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, need_dgrad or need_wgrad, ms(_T.kWeightGroup2, _M.kScale),
+        kn = backend.DGRAD_KN   # dgrad multiplies by the forward FP8 weights as they are: no weight transposes
+        fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, (need_dgrad or need_wgrad) and not kn, ms(_T.kWeightGroup2, _M.kScale),
                                                 ms(_T.kWeightGroup2, _M.kAmax), cache, "fc2", reuse)
         keep_rows = need_wgrad and not need_t     # the row-major FP8 input is the fc1 wgrad operand: it must outlive forward
         if fp8d:
@@ -394,9 +395,9 @@ class _PeerEpMlp(torch.autograd.Function):
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
             # backward never runs
             ctx.gi = ectx.result_tensor(plan.gi_ids[plan.rank], plan.rows_own, hidden) if need_dgrad else None
-            ctx.save_for_backward(input_t_fp8 if need_t else input_keep, fc1_w_t, fc2_w_t, pre_act,
-                                  act_fp8 if need_wgrad else None)
-            ctx.need_t = need_t
+            ctx.save_for_backward(input_t_fp8 if need_t else input_keep, (fc1_w_fp8 if need_dgrad else None) if kn else fc1_w_t,
+                                  fc2_w_fp8 if kn else fc2_w_t, pre_act, act_fp8 if need_wgrad else None)
+            ctx.need_t, ctx.kn = need_t, kn
             metas.set_forward_scale_inv_cloned()
             ctx.metas, ctx.st = metas, st
             ctx.cumsums, ctx.offs, ctx.sizes_cpu = cumsums, offs, sizes_cpu
@@ -489,7 +490,7 @@ class _PeerEpMlp(torch.autograd.Function):
                     backend.grouped_wgrad_rowmajor(grad_out_fp8[r0:r1], act_fp8[r0:r1], _rel(cumsums, j0, j1), dy_si,
                                                    ms(_T.kForwardInputGroup2, _M.kScaleInv, j0), c=grad_fc2[j0:j1])
                 grad_act = backend.fp8_gmm(grad_out_fp8[r0:r1], fc2_w_t[j0:j1], sizes_cpu[j0:j1], dy_si,
-                                           ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), backward=True)
+                                           ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), backward=True, b_is_kn=ctx.kn)
                 backend.grouped_cast_transpose(
                     grad_act, _rel(cumsums, j0, j1), grad_pre_fp8[r0:r1], grad_pre_t[t0:t1] if need_t else None,
                     _rel(offs, j0, j1), ms(_T.kGradOutputGroup2, _M.kScale, j0), ms(_T.kGradOutputGroup2, _M.kAmax, j0),
@@ -497,7 +498,8 @@ class _PeerEpMlp(torch.autograd.Function):
                 dpre_si = ms(_T.kGradOutputGroup2, _M.kScaleInv, j0)
                 if dgrad:
                     backend.fp8_gmm(grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], sizes_cpu[j0:j1], dpre_si,
-                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=gi_local[r0:r1], backward=True)
+                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=gi_local[r0:r1], backward=True,
+                                    b_is_kn=ctx.kn)
             elif wgrad:
                 grad_fc1[j0:j1].zero_()
                 grad_fc2[j0:j1].zero_()
@@ -532,7 +534,7 @@ def forward(module, input, group_sizes, is_first_microbatch, num_chunks):
         # while the host waits for the all-gather of the group sizes.
         metas = Fp8MetaWrapper(mlp.num_groups, mlp.fp8_meta)
         fdt = to_torch_dtype(get_fp8_te_dtype(mlp.fp8_meta["recipe"], fprop_tensor=True))
-        fc1 = cast_weight_cached(mlp.fc1_weight, fdt, want_gi, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
+        fc1 = cast_weight_cached(mlp.fc1_weight, fdt, want_gi and not backend.DGRAD_KN, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
                                  metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax), cache, "fc1", reuse)
         fp8d = bool(getattr(module, "fp8_dispatch", True))
         x_scales = _gather_scales(metas.get_meta_strided(_T.kInputGroup1, _M.kScale), mlp.num_groups, module.group) if fp8d else None

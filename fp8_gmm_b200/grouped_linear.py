@@ -46,16 +46,18 @@ class _GroupedLinear(torch.autograd.Function):
         backend.grouped_cast_transpose(
             input, cumsums, input_fp8, input_t_fp8, offs,
             metas.get_meta_strided(_T.kInputGroup1, _M.kScale), metas.get_meta_strided(_T.kInputGroup1, _M.kAmax))
+        need_wt = need_dgrad and not backend.DGRAD_KN   # weight transposes only for the reference's dgrad dataflow
         weight_fp8, weight_t_fp8 = cast_weight_cached(
-            weight, torch_dtype, need_dgrad, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
+            weight, torch_dtype, need_wt, metas.get_meta_strided(_T.kWeightGroup1, _M.kScale),
             metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax), weight_cache, "weight", reuse_weights)
         out = backend.fp8_gmm(
             input_fp8, weight_fp8, group_sizes,
             metas.get_meta_strided(_T.kInputGroup1, _M.kScaleInv), metas.get_meta_strided(_T.kWeightGroup1, _M.kScaleInv),
             backward=False, cutlass=cutlass)
         if is_grad_enabled:
-            ctx.save_for_backward(input_t_fp8 if need_t else (input_fp8 if need_wgrad else None), weight_t_fp8, group_sizes)
-            ctx.need_t = need_t
+            ctx.save_for_backward(input_t_fp8 if need_t else (input_fp8 if need_wgrad else None),
+                                  weight_t_fp8 if need_wt else (weight_fp8 if need_dgrad else None), group_sizes)
+            ctx.need_t, ctx.need_wt = need_t, need_wt
             ctx.num_groups = num_groups
             metas.set_forward_scale_inv_cloned()
             ctx.fp8_meta_wrapper = metas
@@ -87,7 +89,7 @@ class _GroupedLinear(torch.autograd.Function):
                 grad_out_fp8, weight_t_fp8, group_sizes,
                 metas.get_meta_strided(_T.kGradOutputGroup1, _M.kScaleInv),
                 metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv),
-                backward=True, cutlass=ctx.cutlass)
+                backward=True, cutlass=ctx.cutlass, b_is_kn=not ctx.need_wt)
         grad_weight = None
         if ctx.weight_requires_grad and ctx.need_t:
             grad_weight = backend.grouped_wgrad(

@@ -50,13 +50,14 @@ class _GroupedMlp(torch.autograd.Function):
             backend.blocked_cast(input, input_fp8, perm, x_scale, x_amax, num_groups)
             if need_t:
                 backend.grouped_cast_transpose(input_fp8, cumsums, None, input_t_fp8, offs, None, None)
+        kn = backend.DGRAD_KN   # dgrad multiplies by the forward FP8 weights as they are: no weight transposes
         fc1_w_fp8, fc1_w_t = cast_weight_cached(
-            fc1_weight, torch_dtype, need_dgrad,
+            fc1_weight, torch_dtype, need_dgrad and not kn,
             metas.get_meta_strided(_T.kWeightGroup1, _M.kScale), metas.get_meta_strided(_T.kWeightGroup1, _M.kAmax),
             weight_cache, "fc1", reuse_weights)
         # d(activation) feeds the fc1 weight gradient too, so fc2's transpose is needed whenever anything trains
         fc2_w_fp8, fc2_w_t = cast_weight_cached(
-            fc2_weight, torch_dtype, need_dgrad or need_wgrad,
+            fc2_weight, torch_dtype, (need_dgrad or need_wgrad) and not kn,
             metas.get_meta_strided(_T.kWeightGroup2, _M.kScale), metas.get_meta_strided(_T.kWeightGroup2, _M.kAmax),
             weight_cache, "fc2", reuse_weights)
 
@@ -74,9 +75,10 @@ class _GroupedMlp(torch.autograd.Function):
             metas.get_meta_strided(_T.kInputGroup2, _M.kScaleInv), metas.get_meta_strided(_T.kWeightGroup2, _M.kScaleInv),
             backward=False, c_row_map=None if perm is None else perm.row_map)
         if is_grad_enabled:
-            ctx.save_for_backward(input_t_fp8 if need_t else (input_fp8 if need_wgrad else None), fc1_w_t, fc2_w_t, pre_act,
+            ctx.save_for_backward(input_t_fp8 if need_t else (input_fp8 if need_wgrad else None),
+                                  (fc1_w_fp8 if need_dgrad else None) if kn else fc1_w_t, fc2_w_fp8 if kn else fc2_w_t, pre_act,
                                   act_fp8 if need_wgrad else None, group_sizes)
-            ctx.need_t = need_t
+            ctx.need_t, ctx.kn = need_t, kn
             ctx.num_groups = num_groups
             metas.set_forward_scale_inv_cloned()
             ctx.fp8_meta_wrapper = metas
@@ -129,7 +131,7 @@ class _GroupedMlp(torch.autograd.Function):
                 grad_out_fp8, act_fp8, cumsums, dy_scale_inv, metas.get_meta_strided(_T.kForwardInputGroup2, _M.kScaleInv))
         grad_act = backend.fp8_gmm(
             grad_out_fp8, fc2_w_t, group_sizes, dy_scale_inv,
-            metas.get_meta_strided(_T.kForwardWeightGroup2, _M.kScaleInv), backward=True)
+            metas.get_meta_strided(_T.kForwardWeightGroup2, _M.kScaleInv), backward=True, b_is_kn=ctx.kn)
         # d(activation) fused with the e5m2 cast, the padded transpose and the amax
         grad_pre_fp8 = torch.empty(pre_act.shape, dtype=g_dtype, device=dev)
         grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=g_dtype, device=dev) if need_t else None
@@ -143,7 +145,7 @@ class _GroupedMlp(torch.autograd.Function):
             grad_input = backend.fp8_gmm(
                 grad_pre_fp8, fc1_w_t, group_sizes, dpre_scale_inv,
                 metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv), backward=True,
-                c_row_map=None if perm is None else perm.row_map)
+                c_row_map=None if perm is None else perm.row_map, b_is_kn=ctx.kn)
             if ctx.has_tp:
                 handle = torch.distributed.all_reduce(
                     grad_input, op=torch.distributed.ReduceOp.SUM, group=ctx.tp_group, async_op=True)

@@ -223,6 +223,11 @@ typedef struct {
   const int32_t* c_row_map; /* optional, activation == NONE only: device int32[sum m]; row r of the product is stored
                                at row c_row_map[r] of c (lets the epilogue write straight into a buffer laid out for
                                the combine all-to-all); NULL = identity */
+  int b_layout;             /* 0: b is (G x N x K), contraction contiguous (forward).  1: b is (G x K x N) row-major,
+                               i.e. C_g = A_g B_g without a transpose: what dgrad needs with the forward weights
+                               (G x out x in) as they are -- the tensor cores read B MN-major, so the per-expert
+                               weight transposes of the reference (fp8_gmm/grouped_linear.py:70-73) are not needed.
+                               activation must be NONE. */
 } fp8gmm_gemm_args;
 
 int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* args, void* stream);

@@ -23,11 +23,12 @@ def cuda():
 
 @pytest.fixture(params=["rowmajor", "transposed"])
 def wgrad_dataflow(request):
-    """Runs a module test under both weight-gradient dataflows: operands read row-major by the GEMM (default) and the
-    reference's padded transposes (FP8GMM_WGRAD=transposed)."""
+    """Runs a module test under both backward dataflows: operands read as they lie by the GEMMs (default: row-major
+    activations for wgrad, forward weights for dgrad) and the reference's transposes (FP8GMM_WGRAD=transposed,
+    FP8GMM_DGRAD=transposed)."""
     from fp8_gmm_b200 import backend
 
-    saved = backend.WGRAD_ROWMAJOR
-    backend.WGRAD_ROWMAJOR = request.param == "rowmajor"
+    saved = backend.WGRAD_ROWMAJOR, backend.DGRAD_KN
+    backend.WGRAD_ROWMAJOR = backend.DGRAD_KN = request.param == "rowmajor"
     yield request.param
-    backend.WGRAD_ROWMAJOR = saved
+    backend.WGRAD_ROWMAJOR, backend.DGRAD_KN = saved

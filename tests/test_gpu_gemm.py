@@ -164,6 +164,27 @@ def test_rowmajor_wgrad_equals_the_transposed_path(cuda, sizes, n, k):
             assert (c[g] == 0).all()
 
 
+@pytest.mark.parametrize("sizes,n,k", [([128, 96, 160, 128], 512, 1024), ([5, 0, 33, 130, 257], 256, 272), ([16, 32, 16], 32, 64),
+                                       ([700, 1], 384, 144)])
+@pytest.mark.parametrize("a_dtype", [E4, E5])
+def test_gemm_with_untransposed_weights_equals_the_transposed_path(cuda, sizes, n, k, a_dtype):
+    """b_is_kn=True: B is (G, K, N) and the product is a @ b[g]; same bits as the K-major path on the transposes."""
+    from fp8_gmm_b200 import backend
+
+    G, m = len(sizes), sum(sizes)
+    g = torch.Generator().manual_seed(n + k)
+    a = torch.randint(0, 256, (m, k), generator=g, dtype=torch.uint8)
+    a[(a & 0x7F) >= 0x78] = 0x30
+    b_kn = torch.randint(0, 256, (G, k, n), generator=g, dtype=torch.uint8)
+    b_kn[(b_kn & 0x7F) >= 0x78] = 0x28
+    sa, sb = torch.linspace(0.5, 1.5, G).to(cuda), torch.linspace(0.25, 0.75, G).to(cuda)
+    d_a = a.view(a_dtype).to(cuda)
+    c1 = backend.fp8_gmm(d_a, b_kn.view(E4).to(cuda), torch.tensor(sizes), sa, sb, b_is_kn=True)
+    c2 = backend.fp8_gmm(d_a, b_kn.transpose(1, 2).contiguous().view(E4).to(cuda), torch.tensor(sizes), sa, sb)
+    backend.device_status()
+    assert torch.equal(c1, c2)
+
+
 def test_mixtral_shaped_slice_properties(cuda):
     """Full-size shapes (BASELINE config 2: hidden 4096, ffn 14336) on a slice the oracle cannot afford:
     checked through size-independent properties -- linearity in the per-group scales and agreement of a
