@@ -73,15 +73,16 @@ def even_sizes(groups, rows):
     return sizes
 
 
-def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label):
+def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label, b_is_kn=False):
+    """b_is_kn: B is (G, K, N) and read MN-major (how dgrad consumes the forward weights by default)."""
     G, m = len(sizes), sum(sizes)
     a = rand_fp8((m, k), a_dtype, dev, 1)
-    b = rand_fp8((G, n, k), E4, dev, 2)
+    b = rand_fp8((G, k, n) if b_is_kn else (G, n, k), E4, dev, 2)
     ones = torch.ones(G, device=dev)
     ms_sizes = torch.tensor(sizes)
     if act == "none":
         c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-        fn = lambda: backend.fp8_gmm(a, b, ms_sizes, ones, ones, c=c)  # noqa: E731
+        fn = lambda: backend.fp8_gmm(a, b, ms_sizes, ones, ones, c=c, b_is_kn=b_is_kn)  # noqa: E731
     else:
         n_act = n // 2 if act == "swiglu" else n
         pre = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
@@ -94,7 +95,7 @@ def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label):
     stalls = gemm_stall_profile(backend, fn) if os.environ.get("FP8GMM_BENCH_STALLS") else None
     _, bf16, src = peaks()
     tf = 2.0 * m * n * k / ms / 1e9
-    return {"kernel": "grouped_gemm", "case": label, "stalls": stalls, "groups": G, "rows": m, "n": n, "k": k, "act": act,
+    return {"kernel": "grouped_gemm" + (" (B read MN-major)" if b_is_kn else ""), "case": label, "stalls": stalls, "groups": G, "rows": m, "n": n, "k": k, "act": act,
             "a_format": "e4m3" if a_dtype == E4 else "e5m2", "ms": ms, "tflops": tf, "clocks": LAST_CLOCKS,
             "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
 
@@ -121,21 +122,28 @@ def gemm_stall_profile(backend, fn):
     return out
 
 
-def wgrad_case(backend, dev, sizes, n, k, iters, warmup, label):
+def wgrad_case(backend, dev, sizes, n, k, iters, warmup, label, rowmajor=False):
+    """rowmajor: operands are the row-major activations (read MN-major, the default dataflow); else the reference's
+    padded transposes."""
     from fp8_gmm_b200.utils import cumsum_group_sizes
 
     G, padded, cums, pcs = cumsum_group_sizes(sizes, need_padding=True)
     offs = pcs if padded else cums
-    a_t = rand_fp8((offs[-1] * n,), E5, dev, 3)
-    b_t = rand_fp8((offs[-1] * k,), E4, dev, 4)
     ones = torch.ones(G, device=dev)
     c = torch.empty(G, n, k, dtype=torch.bfloat16, device=dev)
-    fn = lambda: backend.grouped_wgrad(a_t, b_t, offs, n, k, ones, ones, c=c)  # noqa: E731
+    if rowmajor:
+        dy = rand_fp8((cums[-1], n), E5, dev, 3)
+        x = rand_fp8((cums[-1], k), E4, dev, 4)
+        fn = lambda: backend.grouped_wgrad_rowmajor(dy, x, cums, ones, ones, c=c)  # noqa: E731
+    else:
+        a_t = rand_fp8((offs[-1] * n,), E5, dev, 3)
+        b_t = rand_fp8((offs[-1] * k,), E4, dev, 4)
+        fn = lambda: backend.grouped_wgrad(a_t, b_t, offs, n, k, ones, ones, c=c)  # noqa: E731
     ms = time_ms(fn, iters, warmup)
     backend.device_status()
     _, bf16, src = peaks()
     tf = 2.0 * sum(sizes) * n * k / ms / 1e9
-    return {"kernel": "grouped_gemm(wgrad)", "case": label, "groups": G, "rows": sum(sizes), "n": n, "k": k, "ms": ms,
+    return {"kernel": "grouped_gemm(wgrad, " + ("row-major operands" if rowmajor else "padded transposes") + ")", "case": label, "groups": G, "rows": sum(sizes), "n": n, "k": k, "ms": ms,
             "tflops": tf, "clocks": LAST_CLOCKS, "frac_of_2x_bf16_" + src: tf / (2 * bf16), "frac_of_nominal_4500": tf / 4500.0}
 
 
@@ -220,6 +228,9 @@ def main():
     p.add_argument("--max-rows", type=int, default=4096)
     p.add_argument("--cols", type=int, default=7168)
     p.add_argument("--mode", default="cast", choices=["cast", "amax+cast", "transpose", "quantize"])
+    p.add_argument("--dataflow", default="native", choices=["native", "reference"],
+                   help="step-gemms / wgrad: operands as the modules use them by default (forward weights for dgrad, "
+                        "row-major activations for wgrad) or the reference's transposes")
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
     args = p.parse_args()
@@ -236,16 +247,18 @@ def main():
         print(json.dumps(scaled_mm_case(dev, sizes, args.n, args.k, args.iters, args.warmup, "custom")))
     elif args.what == "wgrad":
         sizes = even_sizes(args.groups or 8, args.rows)
-        print(json.dumps(wgrad_case(backend, dev, sizes, args.n, args.k, args.iters, args.warmup, "custom")))
+        print(json.dumps(wgrad_case(backend, dev, sizes, args.n, args.k, args.iters, args.warmup, "custom",
+                                    rowmajor=args.dataflow == "native")))
     elif args.what == "step-gemms":
         sizes, H, F = even_sizes(8, 32768), 4096, 14336
+        nat = args.dataflow == "native"
         for label, fn in [
             ("fc1 fwd + SwiGLU epilogue", lambda: gemm_case(backend, dev, sizes, 2 * F, H, "swiglu", E4, args.iters, args.warmup, "fc1_fwd")),
             ("fc2 fwd", lambda: gemm_case(backend, dev, sizes, H, F, "none", E4, args.iters, args.warmup, "fc2_fwd")),
-            ("fc2 dgrad", lambda: gemm_case(backend, dev, sizes, F, H, "none", E5, args.iters, args.warmup, "fc2_dgrad")),
-            ("fc1 dgrad", lambda: gemm_case(backend, dev, sizes, H, 2 * F, "none", E5, args.iters, args.warmup, "fc1_dgrad")),
-            ("fc2 wgrad", lambda: wgrad_case(backend, dev, sizes, H, F, args.iters, args.warmup, "fc2_wgrad")),
-            ("fc1 wgrad", lambda: wgrad_case(backend, dev, sizes, 2 * F, H, args.iters, args.warmup, "fc1_wgrad")),
+            ("fc2 dgrad", lambda: gemm_case(backend, dev, sizes, F, H, "none", E5, args.iters, args.warmup, "fc2_dgrad", nat)),
+            ("fc1 dgrad", lambda: gemm_case(backend, dev, sizes, H, 2 * F, "none", E5, args.iters, args.warmup, "fc1_dgrad", nat)),
+            ("fc2 wgrad", lambda: wgrad_case(backend, dev, sizes, H, F, args.iters, args.warmup, "fc2_wgrad", nat)),
+            ("fc1 wgrad", lambda: wgrad_case(backend, dev, sizes, 2 * F, H, args.iters, args.warmup, "fc1_wgrad", nat)),
         ]:
             print(json.dumps(fn()), flush=True)
             torch.cuda.empty_cache()

@@ -78,7 +78,6 @@ struct GemmParams {
   int* status;
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
-  int prefetch_kb;     // L2 prefetch distance in K blocks ahead of the shared-memory ring (0 = off)
   int b_mn;            // kModeRows only: B is (G, K, N) row-major, read MN-major through the 3-D map_b (x = n, y = k, z = group)
   int mn_major;        // kModeWgrad only: operands are row-major (rows x features) slices, i.e. MN-major for the MMA
   int super_tiles;     // m-tiles per super-row of the tile order (see decode_tile)
@@ -158,10 +157,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
-}
-__device__ __forceinline__ void prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
-               : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -460,17 +455,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         const int ya = static_cast<int>(t.row0);
         const int yb_mine = rank == 0 ? yb0 : yb1;
         for (int kb = 0; kb < t.num_kb && ok; ++kb) {
-          if (p.prefetch_kb > 0 && kb + p.prefetch_kb < t.num_kb) {
-            // warm L2 for a K block that the ring will only reach later, so its load sees L2 latency, not DRAM's
-            const int xp = (kb + p.prefetch_kb) * kBlockK;
-            prefetch_l2_2d(map_a, xp, ya);
-            if (kCtas == 1) {
-              prefetch_l2_2d(map_b, xp, yb0);
-              prefetch_l2_2d(map_b, xp, yb1);
-            } else {
-              prefetch_l2_2d(map_b, xp, yb_mine);
-            }
-          }
           const long long t0 = p.profile ? clock64() : 0;
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x1);
           if (p.profile) wait_empty += clock64() - t0;
@@ -945,11 +929,6 @@ uint32_t make_idesc(int a_format, int b_format, int ctas, bool a_mn = false, boo
 long long* g_profile = nullptr;
 size_t g_profile_bytes = 0;
 
-int prefetch_distance() {
-  const char* e = getenv("FP8GMM_GEMM_PREFETCH");
-  return e ? atoi(e) : 0;
-}
-
 // Upper bound on the SMs a GEMM launch occupies (fp8gmm_set_gemm_sm_limit; 0 = all).  A persistent grid that
 // fills every SM is delayed as a whole when another kernel (an NCCL exchange on a second stream) holds a few SMs.
 int g_sm_limit = 0;
@@ -960,7 +939,6 @@ int launch(GemmParams& p, int ctas, cudaStream_t s) {
   if (g_sm_limit > 0 && g_sm_limit < sms) sms = g_sm_limit;
   const int workers = sms / ctas > 0 ? sms / ctas : 1;
   const int grid = ctas * (p.total_tiles < workers ? p.total_tiles : workers);
-  p.prefetch_kb = p.b_mn ? 0 : prefetch_distance();  // the experimental prefetch only knows the 2-D operand maps
   p.profile = (g_profile != nullptr && g_profile_bytes >= static_cast<size_t>(grid) * 8 * sizeof(long long)) ? g_profile : nullptr;
   if (ctas == 2) {
     FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
