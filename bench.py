@@ -43,7 +43,7 @@ METRIC = "grouped_mlp_fwd_bwd_fp8_tflops"
 NOMINAL_FP8_TFLOPS = 4500.0
 # DRAM bytes (read + write) per GEMM launch, averaged over the six launches of one Mixtral-shaped step,
 # from the ncu capture summarised in profiles/ (None until a capture exists).
-GEMM_DRAM_BYTES_PER_LAUNCH = 2.842e9  # 17.05 GB over the six launches (profiles/grouped_gemm_mixtral_step_dram_traffic.md)
+GEMM_DRAM_BYTES_PER_LAUNCH = 2.850e9  # 17.10 GB over the six launches (profiles/grouped_gemm_mixtral_step_dram_traffic.md)
 
 
 def parse():
