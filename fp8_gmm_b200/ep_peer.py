@@ -152,6 +152,20 @@ class _Pool:
         self.free.append(i)
 
 
+def resolve_result_buffers(picks, buffers_before):
+    """picks: per rank [out_id, grad_id] as each rank chose from its own free list (-1 = none free, -2 = not wanted).
+    Every rank allocates ``missing`` new buffers (as many as the neediest rank lacks), numbered from
+    ``buffers_before`` on every rank alike, and a rank that lacked buffers takes the new ones in order.  Returns
+    (missing, per-rank [out_id, grad_id] with the -1 entries resolved).  Pure function of what the all-gather
+    delivered, so all ranks reach the same answer."""
+    missing = max((sum(1 for i in pair if i == -1) for pair in picks), default=0)
+    resolved = []
+    for pair in picks:
+        fresh = iter(range(buffers_before, buffers_before + missing))
+        resolved.append([next(fresh) if i == -1 else i for i in pair])
+    return missing, resolved
+
+
 class EpContext:
     """Per (device, group) transport state shared by all ExpertParallelMlp modules: the channel (side stream and
     sequence numbers), the receive buffer for dispatched rows and the pool of result buffers."""
@@ -198,27 +212,15 @@ class EpContext:
         gathered = gathered.cpu()
         plan = PeerPlan(gathered[:, :E].contiguous(), self.rank, num_chunks)
         # collective growth: everybody allocates as many new result buffers as the neediest rank asked for
-        missing = int((gathered[:, E:] == -1).sum(1).max())
+        picks = gathered[:, E:].tolist()
+        n_before = len(pool.buffers)
+        missing, resolved = resolve_result_buffers(picks, n_before)
         new_ids = [pool.grow(int(plan.rows_own_max * 1.25) * row_bytes + 256) for _ in range(missing)]
-        ids = []
-        for i in (out_id, gi_id):
-            if i == -1:
-                i = new_ids.pop(0)
-            ids.append(i)
+        mine = resolved[self.rank]
         for i in new_ids:
-            pool.release(i)
-        out_id, gi_id = ids
-        peer_out = gathered[:, E].tolist()
-        peer_gi = gathered[:, E + 1].tolist()
-        # a rank that asked for new buffers takes them in the same order as above: reconstruct its choice
-        n_before = len(pool.buffers) - missing
-        def resolve(o, g):
-            fresh = list(range(n_before, n_before + missing))
-            res = []
-            for i in (o, g):
-                res.append(fresh.pop(0) if i == -1 else i)
-            return res
-        plan.out_ids, plan.gi_ids = zip(*[resolve(o, g) for o, g in zip(peer_out, peer_gi)])
+            if i not in mine:
+                pool.release(i)
+        plan.out_ids, plan.gi_ids = [r[0] for r in resolved], [r[1] for r in resolved]
         need = plan.rows_local_max * row_bytes
         if self.recv is None or self.recv.nbytes < need:
             # every rank sees the same sizes, so all of them take this branch together

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds
+from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds, resolve_result_buffers
 
 
 def _counts(P, E, seed, zeros=True):
@@ -73,3 +73,13 @@ def test_tapered_and_explicit_chunks_partition_the_experts(El):
     if El >= 16:
         sizes = [b - a for a, b in chunk_bounds(El, "tapered")]
         assert sizes[0] < max(sizes) and sizes[-1] < max(sizes)
+
+
+def test_result_buffer_resolution_is_the_same_on_every_rank():
+    # rank 0 has both buffers, rank 1 lacks the gradient buffer, rank 2 lacks both, rank 3 wants no gradient buffer
+    picks = [[0, 1], [2, -1], [-1, -1], [1, -2]]
+    missing, resolved = resolve_result_buffers(picks, buffers_before=3)
+    assert missing == 2
+    assert resolved == [[0, 1], [2, 3], [3, 4], [1, -2]]
+    assert resolve_result_buffers([[0, 1], [1, 0]], 2) == (0, [[0, 1], [1, 0]])
+    assert resolve_result_buffers([[-1, -2]], 0) == (1, [[0, -2]])
