@@ -6,6 +6,7 @@ routed rows per GPU, delayed scaling with an amax history of 16.  Weak scaling: 
 """
 import json
 import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -71,13 +72,20 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu, E2EPipeline
     dy_dev = dy_host.to(dev)
     recipe = fg.DelayedScaling(amax_history_len=16)
 
+    host = {"fwd": 0.0, "bwd": 0.0, "n": 0}   # host time spent enqueueing (no synchronisation inside)
+
     def step():
         model.mlp.fc1_weight.grad = None
         model.mlp.fc2_weight.grad = None
         x_dev.grad = None
+        t0 = time.perf_counter()
         with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
             out = model(x_dev, sizes)
+        t1 = time.perf_counter()
         out.backward(dy_dev)
+        host["fwd"] += t1 - t0
+        host["bwd"] += time.perf_counter() - t1
+        host["n"] += 1
         return out
 
     def step_on(x_in, dy_in):
@@ -106,8 +114,10 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu, E2EPipeline
     timings = []
     backend.set_gemm_timings(timings)
     launches0 = backend.launch_count()
+    host.update(fwd=0.0, bwd=0.0, n=0)
     with sampler as clocks:
         secs = _timed(step, args.steps, world)
+    host_ms = (host["fwd"] / max(host["n"], 1) * 1e3, host["bwd"] / max(host["n"], 1) * 1e3)
     launches = backend.launch_count() - launches0
     backend.set_gemm_timings(None)
     exposed_ms = None
@@ -185,6 +195,8 @@ def run(args, metric, peaks, ClockSampler, cpu_sample_step, run_cpu, E2EPipeline
                           "ms_per_step_waiting_for_rows_rank0": exposed_ms}
             if exposed_ms is not None:
                 line["ep"]["waits_ms_last_step_rank0"] = last_step_waits
+            # forward includes the host's wait for the size exchange; backward is pure enqueue time
+            line["ep"]["host_ms_per_step_rank0"] = {"forward": host_ms[0], "backward": host_ms[1]}
         if world == 1 and not args.no_cpu_baseline:
             cstep, cflops, desc = cpu_sample_step(H, F, ROWS_PER_EXPERT * 8)
             ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)
