@@ -19,6 +19,7 @@ The plan arithmetic (PeerPlan) is pure host code and is tested on CPU by simulat
 """
 import weakref
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -112,6 +113,18 @@ class PeerPlan:
             self._lists[key] = out
         return self._lists[key]
 
+    def dispatch_arrays(self, chunk):
+        key = ("da", chunk)
+        if key not in self._lists:
+            self._lists[key] = _block_arrays(self.dispatch_blocks(chunk))
+        return self._lists[key]
+
+    def combine_arrays(self, chunk):
+        key = ("ca", chunk)
+        if key not in self._lists:
+            self._lists[key] = _block_arrays(self.combine_blocks(chunk))
+        return self._lists[key]
+
     def combine_blocks(self, chunk):
         """(home rank, dst_row at home, src_row here, rows) for the result rows this rank returns for one chunk."""
         key = ("c", chunk)
@@ -127,6 +140,26 @@ class PeerPlan:
                         out.append((s, send[s][r * El + j], blk[j][s], n))
             self._lists[key] = out
         return self._lists[key]
+
+
+def _block_arrays(blocks):
+    """(peer, dst_row, src_row, rows) tuples -> four int64 numpy arrays."""
+    a = np.asarray(blocks, dtype=np.int64).reshape(-1, 4)
+    return a[:, 0].copy(), a[:, 1].copy(), a[:, 2].copy(), a[:, 3].copy()
+
+
+def _copy_blocks(peer_ptrs, arrays, src_ptr, row_bytes, extra=None):
+    """Copy-block array for one round: rows `src_row..` at `src_ptr` go to row `dst_row` of peer `peer`'s buffer."""
+    peer, dst_row, src_row, rows = arrays
+    n = len(peer) + (0 if extra is None else len(extra))
+    out = np.empty(n, dtype=PeerChannel._BLOCK)
+    m = len(peer)
+    out["dst"][:m] = peer_ptrs[peer] + (dst_row * row_bytes).astype(np.uint64)
+    out["src"][:m] = np.uint64(src_ptr) + (src_row * row_bytes).astype(np.uint64)
+    out["bytes"][:m] = (rows * row_bytes).astype(np.uint64)
+    if extra is not None:
+        out[m:] = extra
+    return out
 
 
 class _Pool:
@@ -189,13 +222,22 @@ class EpContext:
         self.pool = _Pool(device, group)
         self.recv = None
         self._amax_stage = None
+        self._amax_view = None
 
     def amax_stage(self, experts_local):
         """(world x experts_local) fp32 in every rank's memory: row s = rank s's partial amaxes of my experts."""
         need = self.world * experts_local * 4
         if self._amax_stage is None or self._amax_stage.nbytes < need:
             self._amax_stage = PeerBuffer(max(need, 4096), self.device, self.group)
+            self._amax_view = None
         return self._amax_stage
+
+    def amax_stage_tensor(self, experts_local):
+        """The local staging rows as a (world, experts_local) fp32 tensor (built once: a view over foreign memory)."""
+        stage = self.amax_stage(experts_local)
+        if self._amax_view is None or self._amax_view.shape[1] != experts_local:
+            self._amax_view = stage.tensor((self.world, experts_local), torch.float32)
+        return self._amax_view
 
     def plan(self, group_sizes, row_bytes, num_chunks, want_grad_buffer):
         """One small all-gather: everybody's group sizes plus the result buffers each rank picked.  The gather also
@@ -273,15 +315,19 @@ def _amax_blocks(ectx, plan, amax_part, chunk):
     j0, j1 = chunk
     El, r = plan.experts_local, plan.rank
     stage = ectx.amax_stage(El)
-    base = amax_part.data_ptr()
-    return [(stage.ptrs[o] + (r * El + j0) * 4, base + (o * El + j0) * 4, (j1 - j0) * 4) for o in range(plan.world)]
+    out = np.empty(plan.world, dtype=PeerChannel._BLOCK)
+    owners = np.arange(plan.world, dtype=np.uint64)
+    out["dst"] = np.asarray(stage.ptrs, dtype=np.uint64) + np.uint64((r * El + j0) * 4)
+    out["src"] = np.uint64(amax_part.data_ptr()) + (owners * np.uint64(El) + np.uint64(j0)) * np.uint64(4)
+    out["bytes"] = np.uint64((j1 - j0) * 4)
+    return out
 
 
 def _merge_amax(ectx, plan, spec, chunk):
     """Owner side: max-merge the sources' partial amaxes of a chunk into the recipe's amax slots."""
     j0, j1 = chunk
     El = plan.experts_local
-    stage = ectx.amax_stage(El).tensor((plan.world, El), torch.float32)
+    stage = ectx.amax_stage_tensor(El)
     view = _strided_rows(spec, j1 - j0)
     torch.maximum(view, stage[:, j0:j1].amax(dim=0), out=view)
 
@@ -327,13 +373,11 @@ class _PeerEpMlp(torch.autograd.Function):
         else:
             src, amax_part, d_bytes = x, None, row_bytes
         x_ptr = src.data_ptr()
+        recv_np = np.asarray(recv_ptrs, dtype=np.uint64)
 
         def dispatch(chunk):
-            blocks = [(recv_ptrs[o] + d * d_bytes, x_ptr + s * d_bytes, n * d_bytes)
-                      for o, d, s, n in plan.dispatch_blocks(chunk)]
-            if fp8d:
-                blocks += _amax_blocks(ectx, plan, amax_part, chunk)
-            return ch.push(blocks)
+            extra = _amax_blocks(ectx, plan, amax_part, chunk) if fp8d else None
+            return ch.push_arrays(_copy_blocks(recv_np, plan.dispatch_arrays(chunk), x_ptr, d_bytes, extra))
 
         # Every dispatch round is queued now: the rows are ready, and a round that waited for earlier chunks'
         # GEMMs (with which it has nothing to do) would start late and then share the links with the combine rounds.
@@ -360,7 +404,7 @@ class _PeerEpMlp(torch.autograd.Function):
         act_fp8 = torch.empty(rows, ffn, dtype=fdt, device=dev)
         out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
         out = ectx.result_tensor(plan.out_ids[plan.rank], plan.rows_own, hidden)
-        out_ptrs = [ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)]
+        out_np = np.asarray([ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
         last = None
         for c, (j0, j1) in enumerate(chunks):
             ch.wait(seq[c])
@@ -389,9 +433,7 @@ class _PeerEpMlp(torch.autograd.Function):
                     act_fp8[r0:r1], fc2_w_fp8[j0:j1], sizes_cpu[j0:j1],
                     ms(_T.kInputGroup2, _M.kScaleInv, j0), ms(_T.kWeightGroup2, _M.kScaleInv, j0),
                     c=out_local[r0:r1], backward=False)
-            o_ptr = out_local.data_ptr()
-            last = ch_back.push([(out_ptrs[s] + d * row_bytes, o_ptr + l * row_bytes, n * row_bytes)
-                                 for s, d, l, n in plan.combine_blocks((j0, j1))])
+            last = ch_back.push_arrays(_copy_blocks(out_np, plan.combine_arrays((j0, j1)), out_local.data_ptr(), row_bytes))
         ch_back.wait(last)
         if grad_on:
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
@@ -436,13 +478,11 @@ class _PeerEpMlp(torch.autograd.Function):
         else:
             src, amax_part, d_bytes = dy, None, row_bytes
         dy_ptr = src.data_ptr()
+        recv_np = np.asarray(recv_ptrs, dtype=np.uint64)
 
         def dispatch(chunk):
-            blocks = [(recv_ptrs[o] + d * d_bytes, dy_ptr + s * d_bytes, n * d_bytes)
-                      for o, d, s, n in plan.dispatch_blocks(chunk)]
-            if fp8d:
-                blocks += _amax_blocks(ectx, plan, amax_part, chunk)
-            return ch.push(blocks)
+            extra = _amax_blocks(ectx, plan, amax_part, chunk) if fp8d else None
+            return ch.push_arrays(_copy_blocks(recv_np, plan.dispatch_arrays(chunk), dy_ptr, d_bytes, extra))
 
         chunks = plan.chunks
         seq = [dispatch(chunk) for chunk in chunks]   # all rounds up front, as in forward
@@ -463,7 +503,7 @@ class _PeerEpMlp(torch.autograd.Function):
         ctx.gi = None
         if dgrad:
             assert min(plan.gi_ids) >= 0, "input.requires_grad must agree on all ranks"
-            gi_ptrs = [ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)]
+            gi_np = np.asarray([ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
         last = None
         for c, (j0, j1) in enumerate(chunks):
             r0, r1 = cumsums[j0], cumsums[j1]
@@ -506,9 +546,7 @@ class _PeerEpMlp(torch.autograd.Function):
                 grad_fc1[j0:j1].zero_()
                 grad_fc2[j0:j1].zero_()
             if dgrad:
-                g_ptr = gi_local.data_ptr()
-                last = ch_back.push([(gi_ptrs[s] + d * row_bytes, g_ptr + l * row_bytes, n * row_bytes)
-                                     for s, d, l, n in plan.combine_blocks((j0, j1))])
+                last = ch_back.push_arrays(_copy_blocks(gi_np, plan.combine_arrays((j0, j1)), gi_local.data_ptr(), row_bytes))
             else:
                 last = ch_back.push([])
             if live and need_t:

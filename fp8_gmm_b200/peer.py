@@ -10,6 +10,7 @@ and awaited by a one-warp kernel on the receiver's compute stream, says when a r
 """
 import ctypes
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -113,37 +114,44 @@ class PeerChannel:
             arr[r] = self.flags.ptrs[r] + 4 * self.rank       # my word in rank r's page
         self._signal_targets = arr
 
+    _BLOCK = np.dtype([("dst", np.uint64), ("src", np.uint64), ("bytes", np.uint64)])   # layout of fp8gmm_copy_block
+
     def push(self, blocks, after_compute=True):
         """blocks: iterable of (dst_ptr, src_ptr, nbytes).  Returns the sequence number of this round."""
         blocks = [b for b in blocks if b[2] > 0]
-        arr = (CopyBlock * max(len(blocks), 1))()
-        for i, (dst, src, nbytes) in enumerate(blocks):
-            arr[i].dst, arr[i].src, arr[i].bytes = dst, src, nbytes
+        arr = np.empty(len(blocks), dtype=self._BLOCK)
+        if blocks:
+            arr["dst"], arr["src"], arr["bytes"] = zip(*blocks)
+        return self.push_arrays(arr, after_compute)
+
+    def push_arrays(self, arr, after_compute=True):
+        """As push, for a numpy array of copy blocks (dtype ``PeerChannel._BLOCK``; zero-byte entries are skipped by
+        the library): no per-block Python work, which matters when a step issues a few hundred copies."""
+        arr = np.ascontiguousarray(arr)
+        n = len(arr)
         self.seq = (self.seq + 1) & 0xFFFFFFFF
         if after_compute:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
-        s = self.stream.cuda_stream
-        lanes = 1 + len(self.side) if len(blocks) >= 2 * (1 + len(self.side)) else 1
+        base = arr.ctypes.data
+        lanes = 1 + len(self.side) if n >= 2 * (1 + len(self.side)) else 1
+        as_blocks = ctypes.POINTER(CopyBlock)
         if lanes == 1:
-            check(lib.fp8gmm_peer_copy_blocks(arr, len(blocks), s), "peer_copy_blocks")
+            check(lib.fp8gmm_peer_copy_blocks(ctypes.cast(base, as_blocks), n, self.stream.cuda_stream), "peer_copy_blocks")
         else:
             # consecutive blocks usually go to the same peer: deal them out in runs, so that the lanes work on
             # different peers at the same time
             streams = [self.stream] + self.side
             for st in self.side:
                 st.wait_stream(self.stream)
-            run = -(-len(blocks) // lanes)
+            run = -(-n // lanes)
             for k, st in enumerate(streams):
-                part = blocks[k * run:(k + 1) * run]
-                if not part:
-                    continue
-                sub = (CopyBlock * len(part))()
-                for i, (dst, src, nbytes) in enumerate(part):
-                    sub[i].dst, sub[i].src, sub[i].bytes = dst, src, nbytes
-                check(lib.fp8gmm_peer_copy_blocks(sub, len(part), st.cuda_stream), "peer_copy_blocks")
+                lo, hi = k * run, min((k + 1) * run, n)
+                if hi > lo:
+                    check(lib.fp8gmm_peer_copy_blocks(ctypes.cast(base + lo * self._BLOCK.itemsize, as_blocks), hi - lo,
+                                                      st.cuda_stream), "peer_copy_blocks")
             for st in self.side:
                 self.stream.wait_stream(st)
-        check(lib.fp8gmm_peer_signal(self._signal_targets, self.world, self.seq, s), "peer_signal")
+        check(lib.fp8gmm_peer_signal(self._signal_targets, self.world, self.seq, self.stream.cuda_stream), "peer_signal")
         return self.seq
 
     def wait(self, seq):

@@ -104,17 +104,15 @@ class Fp8MetaWrapper:
     def set_forward_scale_inv_cloned(self):
         self._forward_scale_inv_cloned = self._fp8_meta["scaling_fwd"].scale_inv.clone()
 
+    _SLOT_CACHE = {}   # (tensor kind, num_groups) -> (first slot, stride): pure arithmetic, shared by all wrappers
+
     def _resolve(self, fp8_tensor_type, meta_tensor_type):
-        fp8_tensor_type = Fp8TensorType(fp8_tensor_type)
-        if fp8_tensor_type >= Fp8TensorType.kForwardInputGroup1:
+        kind = int(fp8_tensor_type)
+        if kind >= Fp8TensorType.kForwardInputGroup1:
             assert meta_tensor_type == MetaTensorType.kScaleInv
             meta_tensor = self._forward_scale_inv_cloned
         else:
-            meta = (
-                self._fp8_meta["scaling_fwd"]
-                if fp8_tensor_type < Fp8TensorType.kGradOutputGroup1
-                else self._fp8_meta["scaling_bwd"]
-            )
+            meta = self._fp8_meta["scaling_fwd"] if kind < Fp8TensorType.kGradOutputGroup1 else self._fp8_meta["scaling_bwd"]
             if meta_tensor_type == MetaTensorType.kScale:
                 meta_tensor = meta.scale
             elif meta_tensor_type == MetaTensorType.kScaleInv:
@@ -122,11 +120,15 @@ class Fp8MetaWrapper:
             else:
                 meta_tensor = meta.amax_history[0]
         assert meta_tensor is not None
-        name = fp8_tensor_type.name
-        group_offset = 0 if "Group1" in name else self._num_groups
-        stage = self._BACKWARD_OFFSET if "GradOutput" in name else self._FORWARD_OFFSET
-        type_offset = 1 if "Weight" in name else 0
-        return meta_tensor, group_offset * stage + type_offset, stage
+        key = (kind, self._num_groups)
+        slot = self._SLOT_CACHE.get(key)
+        if slot is None:
+            name = Fp8TensorType(kind).name
+            group_offset = 0 if "Group1" in name else self._num_groups
+            stage = self._BACKWARD_OFFSET if "GradOutput" in name else self._FORWARD_OFFSET
+            type_offset = 1 if "Weight" in name else 0
+            slot = self._SLOT_CACHE[key] = (group_offset * stage + type_offset, stage)
+        return meta_tensor, slot[0], slot[1]
 
     def get_meta_tensors(self, fp8_tensor_type, meta_tensor_type):
         """List of 0-dim views, one per group (the reference's return type)."""
