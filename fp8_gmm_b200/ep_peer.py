@@ -25,6 +25,7 @@ import torch.distributed as dist
 
 from . import backend
 from .grouped_linear import cast_weight_cached
+from ._lib import check, lib
 from .peer import PeerBuffer, PeerChannel
 from .recipe import get_fp8_te_dtype
 from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_sizes, to_torch_dtype
@@ -219,6 +220,12 @@ class EpContext:
         # (four copy lanes each: blocks of 8-16 MiB moved 8-9 % faster than over one lane in a 4-GPU all-to-all pattern)
         self.channel = PeerChannel(device, group, copy_streams=4)          # dispatch rounds
         self.channel_back = PeerChannel(device, group, copy_streams=4)     # combine rounds
+        # "My buffers are free" announcements (signals only, no copies) and a host-side group for the size exchange:
+        # together they replace a device all-gather + host synchronisation per step, so the host may run a step ahead
+        # of the GPU and a late host on one rank does not stall the others' GPUs.  A sub-group keeps the device gather
+        # (creating a gloo group is collective over all ranks of the job).
+        self.ready = PeerChannel(device, group)
+        self.host_group = dist.new_group(backend="gloo") if group is None else None
         self.pool = _Pool(device, group)
         self.recv = None
         self._amax_stage = None
@@ -240,18 +247,28 @@ class EpContext:
         return self._amax_view
 
     def plan(self, group_sizes, row_bytes, num_chunks, want_grad_buffer):
-        """One small all-gather: everybody's group sizes plus the result buffers each rank picked.  The gather also
-        orders this step's pushes after every rank's previous use of the buffers they land in."""
+        """One small all-gather (host side): everybody's group sizes plus the result buffers each rank picked."""
         E = group_sizes.numel()
         own_bytes = int(group_sizes.sum()) * row_bytes
         pool = self.pool
         out_id = pool.pick(own_bytes)
         gi_id = pool.pick(own_bytes) if want_grad_buffer else -2
         meta = torch.cat([group_sizes.to(torch.int64), torch.tensor([out_id, gi_id], dtype=torch.int64)])
-        mine = meta.to(self.device, non_blocking=True)
-        gathered = torch.empty(self.world, E + 2, dtype=torch.int64, device=self.device)
-        dist.all_gather_into_tensor(gathered, mine, group=self.group)
-        gathered = gathered.cpu()
+        if self.host_group is not None:
+            parts = [torch.empty_like(meta) for _ in range(self.world)]
+            dist.all_gather(parts, meta, group=self.host_group)      # host to host: the GPU is not waited for
+            gathered = torch.stack(parts)
+        else:
+            mine = meta.to(self.device, non_blocking=True)
+            gathered = torch.empty(self.world, E + 2, dtype=torch.int64, device=self.device)
+            dist.all_gather_into_tensor(gathered, mine, group=self.group)
+            gathered = gathered.cpu()
+        # Device-side ordering of this step's pushes after every rank's previous use of the buffers they land in:
+        # each rank announces, after all the work its compute stream holds so far, that its buffers are free; both
+        # copy streams wait for everybody's announcement before their next copy.
+        free_seq = self.ready.push_arrays(np.empty(0, dtype=PeerChannel._BLOCK))
+        for ch in (self.channel, self.channel_back):
+            check(lib.fp8gmm_peer_wait(self.ready.flags.local, self.world, free_seq, ch.stream.cuda_stream), "peer_wait")
         plan = PeerPlan(gathered[:, :E].contiguous(), self.rank, num_chunks)
         # collective growth: everybody allocates as many new result buffers as the neediest rank asked for
         picks = gathered[:, E:].tolist()
