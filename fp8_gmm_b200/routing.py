@@ -13,10 +13,7 @@ calls are provided here on this package's kernels (fp8_gmm_b200/csrc/routing.cu)
 import torch
 
 from ._lib import check, lib
-
-
-def _stream():
-    return torch.cuda.current_stream().cuda_stream
+from .backend import _stream
 
 
 class Routing:
