@@ -27,9 +27,6 @@ class Routing:
         self.tokens_per_expert, self.inverse = tokens_per_expert, inverse
 
 
-_inverse_of = {}   # id(indices tensor) -> inverse permutation, so the megablocks-style calls need no extra argument
-
-
 def sort_by_expert(top_expert, n_experts):
     """top_expert: CUDA integer tensor with tokens * top_k expert ids (flattened token-major).  Returns a Routing."""
     ids = top_expert.reshape(-1).to(torch.int32).contiguous()
@@ -43,6 +40,8 @@ def sort_by_expert(top_expert, n_experts):
     hist = torch.empty(n_experts, dtype=torch.int64, device=dev)
     check(lib.fp8gmm_moe_sort(ids.data_ptr(), n, n_experts, indices.data_ptr(), bin_ids.data_ptr(), inverse.data_ptr(),
                               bins.data_ptr(), hist.data_ptr(), _stream()), "moe_sort")
+    # the megablocks-style calls below only pass `indices` on: let it carry its inverse permutation
+    indices._fp8gmm_inverse = inverse
     return Routing(indices, bin_ids, bins, hist, inverse)
 
 
@@ -50,18 +49,14 @@ def indices_and_bins(top_expert, n_experts, sort_end_bit=None):
     """Same return order as the reference example's helper (fp8_gmm/example.py:26-32): indices, bin_ids, bins,
     tokens_per_expert.  ``sort_end_bit`` is accepted and ignored (the counting sort needs no bit count)."""
     r = sort_by_expert(top_expert, n_experts)
-    _inverse_of[id(r.indices)] = (r.indices, r.inverse)
-    if len(_inverse_of) > 64:
-        _inverse_of.pop(next(iter(_inverse_of)))
     return r.indices, r.bin_ids, r.bins, r.tokens_per_expert
 
 
 def _inverse(indices):
-    hit = _inverse_of.get(id(indices))
-    if hit is not None and hit[0] is indices:
-        return hit[1]
-    inv = torch.empty_like(indices)
-    inv[indices.long()] = torch.arange(indices.numel(), dtype=indices.dtype, device=indices.device)
+    inv = getattr(indices, "_fp8gmm_inverse", None)
+    if inv is None:  # an `indices` tensor that did not come from sort_by_expert: invert it here
+        inv = torch.empty_like(indices)
+        inv[indices.long()] = torch.arange(indices.numel(), dtype=indices.dtype, device=indices.device)
     return inv
 
 
