@@ -92,7 +92,8 @@ struct GemmParams {
   int total_tiles;
   uint32_t idesc;
   int tile_start[kMaxGroups + 1];  // prefix sum of tiles per group
-  int row_start[kMaxGroups + 1];   // kModeRows: prefix sum of rows; kModeWgrad: t_offsets (contraction offsets)
+  int row_start[kMaxGroups + 1];   // kModeRows: first row of the group's slice; kModeWgrad: t_offsets (contraction offsets)
+  int row_count[kMaxGroups];       // kModeRows: rows of the group this launch covers (a launch may leave a tail to another)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -277,7 +278,7 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile, i
   const int local = tile - p.tile_start[g];
   int rows_g, contraction;
   if (p.mode == kModeRows) {
-    rows_g = p.row_start[g + 1] - p.row_start[g];
+    rows_g = p.row_count[g];
     contraction = p.k;
   } else {
     rows_g = p.m_fixed;
@@ -999,17 +1000,28 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   int ctas = forced_ctas();
   if (ctas == 0) ctas = (pad256 * 10 <= pad128 * 11) ? 2 : 1;
   const int tile_m = kBlockM * ctas;
-  int64_t rows = 0, tiles = 0;
+  // With paired tiles a group whose last 256-row tile holds at most 128 rows would spend a whole pair tile on them
+  // (every n-tile of it): such tails are left to a second launch of the single-CTA kernel, whose 128-row tile fits.
+  const bool split_tails = ctas == 2 && getenv("FP8GMM_GEMM_NO_TAIL_SPLIT") == nullptr;
+  int tail_start[kMaxGroups], tail_count[kMaxGroups];
+  int64_t rows = 0, tiles = 0, tail_tiles = 0;
   p.tile_start[0] = 0;
-  p.row_start[0] = 0;
   for (int g = 0; g < a->num_groups; ++g) {
     const int64_t m = a->m_sizes[g];
+    const int64_t rem = m % (2 * kBlockM);
+    const int64_t tail = (split_tails && rem > 0 && rem <= kBlockM) ? rem : 0;
+    const int64_t main_rows = m - tail;
+    p.row_start[g] = static_cast<int>(rows);
+    p.row_count[g] = static_cast<int>(main_rows);
+    tail_start[g] = static_cast<int>(rows + main_rows);
+    tail_count[g] = static_cast<int>(tail);
     rows += m;
-    tiles += ((m + tile_m - 1) / tile_m) * tiles_n;
+    tiles += ((main_rows + tile_m - 1) / tile_m) * tiles_n;
+    tail_tiles += (tail > 0 ? 1 : 0) * tiles_n;
     FP8GMM_CHECK_ARG(rows <= INT32_MAX - 1024 && tiles <= INT32_MAX / 2, "grouped_gemm: problem too large");
-    p.row_start[g + 1] = static_cast<int>(rows);
     p.tile_start[g + 1] = static_cast<int>(tiles);
   }
+  p.row_start[a->num_groups] = static_cast<int>(rows);
   if (rows == 0) return FP8GMM_OK;
   FP8GMM_CHECK_ARG(a->a && a->b && a->c, "grouped_gemm: NULL operand pointer");
   FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a) | reinterpret_cast<uintptr_t>(a->b) |
@@ -1059,7 +1071,27 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
     if (rc != FP8GMM_OK) return rc;
     p.tma_store = 1;
   }
-  return launch(p, ctas, static_cast<cudaStream_t>(stream));
+  if (p.total_tiles > 0) {
+    rc = launch(p, ctas, static_cast<cudaStream_t>(stream));
+    if (rc != FP8GMM_OK) return rc;
+  }
+  if (tail_tiles > 0) {
+    // second launch: the groups' short tails on 128-row tiles (same operands, maps and epilogue)
+    int t = 0;
+    for (int g = 0; g < a->num_groups; ++g) {
+      p.row_start[g] = tail_start[g];
+      p.row_count[g] = tail_count[g];
+      p.tile_start[g] = t;
+      t += (tail_count[g] > 0 ? 1 : 0) * static_cast<int>(tiles_n);
+    }
+    p.tile_start[a->num_groups] = t;
+    p.total_tiles = t;
+    p.idesc = make_idesc(a->a_format, a->b_format, 1, false, a->b_layout == 1);
+    p.super_tiles = (a->k > kLongK ? kSuperRowsLongK : kSuperRowsShortK) / kBlockM;
+    rc = launch(p, 1, static_cast<cudaStream_t>(stream));
+    if (rc != FP8GMM_OK) return rc;
+  }
+  return FP8GMM_OK;
 }
 
 int fp8gmm_set_gemm_sm_limit(int sms) {
