@@ -355,7 +355,8 @@ def run_single(args):
                 "how": "GroupedMlp forward + backward per step; inputs copied from pinned host memory and results read "
                        "back every step on side streams (next step's inputs prefetched during this step's compute)"},
         "gpu_launches": int(launches),
-        "roofline": {"kernel": "grouped_gemm_kernel (tcgen05, 6 launches per step)", "bound": "tensor",
+        "roofline": {"kernel": "grouped_gemm_pair_kernel (tcgen05; 6 GEMM calls per step, events around each call; the four "
+                               "forward/dgrad calls add a short grouped_gemm_kernel launch for the groups' tails)", "bound": "tensor",
                      "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s", "frac": achieved / peak_fp8,
                      "peak_source": f"2 x {peaks['source']} dense bf16 sustained ({peaks['bf16_sustained']} TFLOP/s)",
                      "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
