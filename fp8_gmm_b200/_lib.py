@@ -97,7 +97,9 @@ SYMBOLS = {
     "fp8gmm_grouped_wgrad_static": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_grouped_wgrad_rowmajor": (ctypes.c_int, [ctypes.POINTER(WgradArgs), c_vp]),
     "fp8gmm_set_gemm_sm_limit": (ctypes.c_int, [ctypes.c_int]),
-    "fp8gmm_set_gemm_profile_buffer": (ctypes.c_int, [c_vp, ctypes.c_size_t]),
+    "fp8gmm_set_gemm_variant": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "fp8gmm_device_status_async": (ctypes.c_int, [c_vp, c_vp]),
+    "fp8gmm_set_wait_limits": (ctypes.c_int, [c_i64, c_i64]),
     "fp8gmm_moe_sort": (ctypes.c_int, [c_vp, c_i64, ctypes.c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "fp8gmm_moe_gather": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),
     "fp8gmm_moe_scatter": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),

@@ -61,6 +61,17 @@ def set_gemm_sm_limit(sms):
     check(lib.fp8gmm_set_gemm_sm_limit(int(sms)), "set_gemm_sm_limit")
 
 
+def set_gemm_variant(ctas=0, tail_split=True, tma_epilogue=True):
+    """Force the GEMM tile shape (1 = single-CTA 128-row tiles, 2 = CTA-pair 256-row tiles, 0 = automatic) and the
+    two launch switches; see fp8gmm_set_gemm_variant.  For tests and experiments: results are bit-identical."""
+    check(lib.fp8gmm_set_gemm_variant(int(ctas), int(bool(tail_split)), int(bool(tma_epilogue))), "set_gemm_variant")
+
+
+def set_wait_limits(gemm_wait_s=0.0, peer_wait_s=0.0):
+    """Limits of the kernels' bounded waits in seconds (0 keeps the current value); see fp8gmm_set_wait_limits."""
+    check(lib.fp8gmm_set_wait_limits(int(gemm_wait_s * 1e9), int(peer_wait_s * 1e9)), "set_wait_limits")
+
+
 def launch_count():
     """Kernels launched by the C-ABI library in this process so far."""
     return int(lib.fp8gmm_launch_count())
@@ -551,3 +562,22 @@ def delayed_scaling_update(amax_history, scale, scale_inv, fp8_max, margin=0, al
 def device_status():
     """Synchronise the current stream and raise if a kernel reported a bounded wait that ran out."""
     check(lib.fp8gmm_device_status(_stream()), "device_status")
+
+
+class StatusWatch:
+    """Non-blocking view of the device status word for training loops: ``record()`` enqueues a copy of the word
+    into page-locked host memory on the current stream, ``check()`` raises if a copy that has already landed shows
+    that a bounded wait ran out (the outputs of that launch, and everything computed from them, are undefined)."""
+
+    def __init__(self):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    def record(self):
+        check(lib.fp8gmm_device_status_async(self.host.data_ptr(), _stream()), "device_status_async")
+
+    def check(self):
+        code = int(self.host[0])
+        if code != 0:
+            raise RuntimeError(
+                f"fp8_gmm_b200: a kernel gave up on a bounded wait in an earlier step (status 0x{code:x}: a peer was "
+                "late or a copy never arrived); results since then are undefined")

@@ -18,6 +18,8 @@ int cuda_fail(cudaError_t err, const char* what);
 int sm_count();              // SMs of the current device (cached per device)
 int* device_status_word();   // device address of the per-device status word (kernels report timeouts here)
 void count_launch();         // bumps the process-wide launch counter (fp8gmm_launch_count)
+unsigned long long gemm_wait_limit_ns();  // limit of the GEMM kernels' mbarrier waits (fp8gmm_set_wait_limits)
+unsigned long long peer_wait_limit_ns();  // limit of fp8gmm_peer_wait's spin on the sequence numbers
 
 #define FP8GMM_CHECK_ARG(cond, ...)       \
   do {                                    \

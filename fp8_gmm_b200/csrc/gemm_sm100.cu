@@ -57,7 +57,6 @@ constexpr int kTileABytes = kBlockM * kBlockK;          // 16 KiB
 constexpr int kTileBBytes = kBlockN * kBlockK;          // 32 KiB
 constexpr int kTmemCols = 512;
 constexpr int kMaxGroups = 512;
-constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 enum GemmMode { kModeRows = 0, kModeWgrad = 1 };
 
@@ -77,7 +76,7 @@ struct GemmParams {
   int64_t ld_act;  // row pitch of act_out in bytes
   int* status;
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
-  long long* profile;  // optional: per-CTA stall counters (see fp8gmm_set_gemm_profile_buffer), else NULL
+  unsigned long long wait_ns;  // limit of every mbarrier wait (fp8gmm_set_wait_limits)
   int b_mn;            // kModeRows only: B is (G, K, N) row-major, read MN-major through the 3-D map_b (x = n, y = k, z = group)
   int mn_major;        // kModeWgrad only: operands are row-major (rows x features) slices, i.e. MN-major for the MMA
   int super_tiles;     // m-tiles per super-row of the tile order (see decode_tile)
@@ -128,23 +127,25 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Bounded wait.  Returns false (after raising the CTA abort flag and recording `code`) when the barrier
-// did not complete its phase within kWaitLimitNs, or when another role already aborted.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// did not complete its phase within `limit_ns`, or when another role already aborted.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                            unsigned long long limit_ns) {
   const unsigned long long t0 = global_ns();
   for (;;) {
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitLimitNs) {
+    if (global_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       atomicOr(status, code);
       return false;
     }
   }
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+  return mbar_wait_slow(bar, parity, abort_flag, status, code, limit_ns);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
@@ -161,6 +162,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+// A tensor map that lives in global memory and was written through the generic proxy (here: by a host-to-device
+// copy that precedes the kernel on its stream) must be acquired by the thread that hands it to the TMA unit before
+// its first use; system scope because the writer was not this GPU's SMs.
+__device__ __forceinline__ void acquire_tensormap(const CUtensorMap* map) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
 // ---- TMA store of a staged (32 rows x 128 bytes, SWIZZLE_128B) box -------------------------------
@@ -436,12 +443,17 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      long long wait_empty = 0;
+      int acquired_group = -1;
       const uint32_t full0_leader = kCtas == 2 ? map_to_cta(full_bar(0), 0) : 0;
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
         const TileInfo t = decode_tile<kCtas>(p, tile, rank);
         const CUtensorMap* map_a = p.mode == kModeRows ? &p.map_a : &p.maps[2 * t.group];
         const CUtensorMap* map_b = p.mode == kModeRows ? &p.map_b : &p.maps[2 * t.group + 1];
+        if (p.mode == kModeWgrad && t.group != acquired_group && t.num_kb > 0) {
+          acquire_tensormap(map_a);
+          acquire_tensormap(map_b);
+          acquired_group = t.group;
+        }
         // first B row of each 128-row box this CTA loads: 1 CTA -> two boxes (columns [0,128) and [128,256) of the
         // tile); pair -> one box, the half selected by `rank`.  SwiGLU: first half = gate rows, second = up rows.
         int yb0, yb1;
@@ -456,9 +468,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         const int ya = static_cast<int>(t.row0);
         const int yb_mine = rank == 0 ? yb0 : yb1;
         for (int kb = 0; kb < t.num_kb && ok; ++kb) {
-          const long long t0 = p.profile ? clock64() : 0;
-          ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x1);
-          if (p.profile) wait_empty += clock64() - t0;
+          ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 0x1, p.wait_ns);
           if (ok) {
             const uint32_t sa = tiles_addr + stage * kStageBytes;
             const uint32_t sb = sa + kTileABytes;
@@ -494,7 +504,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
           }
         }
       }
-      if (p.profile) p.profile[blockIdx.x * 8 + 0] = wait_empty;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -507,9 +516,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      long long wait_full = 0, wait_tempty = 0, issue = 0;
-      const long long t_begin = p.profile ? clock64() : 0;
-      const unsigned long long ns_begin = p.profile ? global_ns() : 0;
       const bool a_mn = p.mn_major != 0, b_mn = p.mn_major != 0 || p.b_mn != 0;
       const uint64_t desc_a0 = a_mn ? make_smem_desc_mn(tiles_addr, 16) : make_smem_desc(tiles_addr);
       const uint64_t desc_b0 = b_mn ? make_smem_desc_mn(tiles_addr + kTileABytes, kTileBBytes / 2) : make_smem_desc(tiles_addr + kTileABytes);
@@ -520,17 +526,13 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
         const TileInfo t = decode_tile<kCtas>(p, tile, rank);
         if (t.num_kb == 0) continue;  // empty contraction: the epilogue writes zeros on its own
-        const long long t0 = p.profile ? clock64() : 0;
-        ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x2);
-        if (p.profile) wait_tempty += clock64() - t0;
+        ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 0x2, p.wait_ns);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * kBlockN);
         for (int kb = 0; kb < t.num_kb; ++kb) {
-          const long long t1 = p.profile ? clock64() : 0;
-          ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, 0x4);
+          ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, 0x4, p.wait_ns);
           if (!ok) break;
-          const long long t2 = p.profile ? clock64() : 0;
           // descriptors of this stage: the start-address field counts 16-byte units
           const uint64_t da = desc_a0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
           const uint64_t db = desc_b0 + static_cast<uint64_t>(stage * (kStageBytes >> 4));
@@ -543,10 +545,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
               umma_f8_pair(tmem_d, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           if (kCtas == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage));
-          if (p.profile) {
-            wait_full += t2 - t1;
-            issue += clock64() - t2;
-          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -557,13 +555,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
-      if (p.profile) {
-        p.profile[blockIdx.x * 8 + 1] = wait_full;
-        p.profile[blockIdx.x * 8 + 2] = wait_tempty;
-        p.profile[blockIdx.x * 8 + 3] = clock64() - t_begin;
-        p.profile[blockIdx.x * 8 + 6] = issue;
-        p.profile[blockIdx.x * 8 + 7] = static_cast<long long>(global_ns() - ns_begin);
-      }
     }
     __syncwarp();
   } else {
@@ -573,7 +564,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    long long wait_tfull = 0, busy = 0;
     for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
       const TileInfo t = decode_tile<kCtas>(p, tile, rank);
       const bool row_ok = row_in_tile < t.valid_rows;
@@ -587,12 +577,9 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         }
         continue;
       }
-      const long long t0 = p.profile ? clock64() : 0;
-      if (lane == 0) ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x8);
+      if (lane == 0) ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 0x8, p.wait_ns);
       ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
       if (!ok) break;
-      const long long t1 = p.profile ? clock64() : 0;
-      wait_tfull += t1 - t0;
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * kBlockN) + (static_cast<uint32_t>(quad * 32) << 16);
 
@@ -787,15 +774,10 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       if (lane == 0) {
         if (kCtas == 1) mbar_arrive(tempty_bar(acc)); else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
       }
-      if (p.profile) busy += clock64() - t1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
     if (lane == 0) bulk_wait_all();  // TMA stores of this warp have been written out
-    if (p.profile && warp == 2 && lane == 0) {
-      p.profile[blockIdx.x * 8 + 4] = wait_tfull;
-      p.profile[blockIdx.x * 8 + 5] = busy;
-    }
   }
 
   // ===================== teardown =====================
@@ -905,11 +887,25 @@ int encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return FP8GMM_OK;
 }
 
-// FP8GMM_GEMM_EPILOGUE=direct switches the TMA-store epilogue off (every row is then written with per-thread
-// 16-byte stores); for experiments.
-bool tma_epilogue_enabled() {
-  const char* e = getenv("FP8GMM_GEMM_EPILOGUE");
-  return !(e != nullptr && e[0] == 'd');
+// Process-wide switches of the GEMM launches.  Defaults come from the environment, read once when the library is
+// first used (FP8GMM_GEMM_CTAS=1|2 forces the tile shape, FP8GMM_GEMM_EPILOGUE=direct turns the TMA-store epilogue
+// off, FP8GMM_GEMM_NO_TAIL_SPLIT keeps short group tails on pair tiles); fp8gmm_set_gemm_variant changes them later.
+struct Tuning {
+  int ctas = 0;             // 0 = choose per call, 1 = single-CTA 128-row tiles, 2 = CTA-pair 256-row tiles
+  bool tail_split = true;   // pair tiles: tails of at most 128 rows go to a second launch on 128-row tiles
+  bool tma_epilogue = true; // full 32-row slabs leave through shared memory + TMA stores
+};
+Tuning& tuning() {
+  static Tuning t = [] {
+    Tuning v;
+    const char* e = getenv("FP8GMM_GEMM_CTAS");
+    if (e != nullptr) v.ctas = e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0;
+    e = getenv("FP8GMM_GEMM_EPILOGUE");
+    v.tma_epilogue = !(e != nullptr && e[0] == 'd');
+    v.tail_split = getenv("FP8GMM_GEMM_NO_TAIL_SPLIT") == nullptr;
+    return v;
+  }();
+  return t;
 }
 
 uint32_t make_idesc(int a_format, int b_format, int ctas, bool a_mn = false, bool b_mn = false) {
@@ -926,10 +922,6 @@ uint32_t make_idesc(int a_format, int b_format, int ctas, bool a_mn = false, boo
   return d;
 }
 
-// Profiling buffer installed with fp8gmm_set_gemm_profile_buffer (process-wide, NULL = off).
-long long* g_profile = nullptr;
-size_t g_profile_bytes = 0;
-
 // Upper bound on the SMs a GEMM launch occupies (fp8gmm_set_gemm_sm_limit; 0 = all).  A persistent grid that
 // fills every SM is delayed as a whole when another kernel (an NCCL exchange on a second stream) holds a few SMs.
 int g_sm_limit = 0;
@@ -940,7 +932,7 @@ int launch(GemmParams& p, int ctas, cudaStream_t s) {
   if (g_sm_limit > 0 && g_sm_limit < sms) sms = g_sm_limit;
   const int workers = sms / ctas > 0 ? sms / ctas : 1;
   const int grid = ctas * (p.total_tiles < workers ? p.total_tiles : workers);
-  p.profile = (g_profile != nullptr && g_profile_bytes >= static_cast<size_t>(grid) * 8 * sizeof(long long)) ? g_profile : nullptr;
+  p.wait_ns = gemm_wait_limit_ns();
   if (ctas == 2) {
     FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
     grouped_gemm_pair_kernel<<<grid, kThreads, Cfg<2>::kSmemBytes, s>>>(p);
@@ -953,14 +945,122 @@ int launch(GemmParams& p, int ctas, cudaStream_t s) {
   return FP8GMM_OK;
 }
 
-// 0 = choose automatically, 1 / 2 = force single-CTA / paired tiles (FP8GMM_GEMM_CTAS, for experiments).
-int forced_ctas() {
-  const char* e = getenv("FP8GMM_GEMM_CTAS");
-  if (e == nullptr) return 0;
-  return e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0;
+bool fmt_ok(int f) { return f == FP8GMM_E4M3 || f == FP8GMM_E5M2; }
+
+// ---------------------------------------------------------------------------------------------
+// Weight gradients: one host routine behind the three entry points
+// ---------------------------------------------------------------------------------------------
+enum WgradForm {
+  kWgradTransposed,  // operands are the padded-transposed blocks (features x L_g), K-major for the MMA
+  kWgradRowMajor     // operands are row slices of the row-major activations (L_g x features), MN-major for the MMA
+};
+
+// Validates the arguments, encodes one pair of tensor maps per group into `host_maps` (2 * num_groups entries of
+// host memory owned by the caller), copies them to `device_maps` on `s` and launches the kernel.  The copy reads
+// `host_maps` from ordinary host memory that the caller releases right after this returns, which a captured graph
+// would replay from a dead buffer: the call is refused while `s` is being captured.
+int wgrad_launch(const fp8gmm_wgrad_args* a, cudaStream_t s, const char* name, WgradForm form, CUtensorMap* device_maps,
+                 CUtensorMap* host_maps) {
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  FP8GMM_CHECK_CUDA(cudaStreamIsCapturing(s, &capture));
+  if (capture != cudaStreamCaptureStatusNone) {
+    set_error("%s: the stream is being captured; this call stages its per-group descriptors with a copy from temporary "
+              "host memory and cannot be part of a CUDA graph", name);
+    return FP8GMM_UNSUPPORTED;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int ctas = tuning().ctas;
+  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
+  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
+  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
+  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "%s: problem too large", name);
+  memset(host_maps, 0, sizeof(CUtensorMap) * 2 * static_cast<size_t>(a->num_groups));
+  p.tile_start[0] = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
+    const int64_t len = o1 - o0;
+    FP8GMM_CHECK_ARG(len >= 0 && o1 <= INT32_MAX - 1024, "%s: group %d has a negative or oversized range", name, g);
+    FP8GMM_CHECK_ARG(form == kWgradRowMajor || len % 16 == 0,
+                     "%s: group %d contraction length %lld must be a multiple of 16", name, g, (long long)len);
+    p.row_start[g] = static_cast<int>(o0);
+    p.row_start[g + 1] = static_cast<int>(o1);
+    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
+    if (len > 0) {
+      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "%s: NULL operand pointer", name);
+      const char* base_a = static_cast<const char*>(a->a_t) + o0 * a->n;
+      const char* base_b = static_cast<const char*>(a->b_t) + o0 * a->k;
+      // transposed: (features x len) bytes; row-major: (len x features) bytes -- the box is 128 x 128 bytes either way
+      const bool t = form == kWgradTransposed;
+      int rc = encode_map(&host_maps[2 * g], base_a, static_cast<uint64_t>(t ? a->n : len), static_cast<uint64_t>(t ? len : a->n));
+      if (rc != FP8GMM_OK) return rc;
+      rc = encode_map(&host_maps[2 * g + 1], base_b, static_cast<uint64_t>(t ? a->k : len), static_cast<uint64_t>(t ? len : a->k));
+      if (rc != FP8GMM_OK) return rc;
+    }
+  }
+  // Every descriptor slot this launch reads is rewritten (empty groups get zeroed slots that are never used).  The
+  // source is pageable, so the runtime has staged the bytes by the time the call returns.
+  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(device_maps, host_maps, sizeof(CUtensorMap) * 2 * static_cast<size_t>(a->num_groups),
+                                    cudaMemcpyHostToDevice, s));
+  p.maps = device_maps;
+  p.c = static_cast<uint16_t*>(a->c);
+  p.sa = a->a_scale_inv;
+  p.sb = a->b_scale_inv;
+  p.sa_stride = a->a_scale_inv_stride;
+  p.sb_stride = a->b_scale_inv_stride;
+  p.ldc = a->k;
+  p.status = device_status_word();
+  FP8GMM_CHECK_ARG(p.status != nullptr, "%s: cannot resolve the device status word", name);
+  p.mode = kModeWgrad;
+  p.mn_major = form == kWgradRowMajor ? 1 : 0;
+  p.activation = FP8GMM_ACT_NONE;
+  p.num_groups = a->num_groups;
+  p.n = static_cast<int>(a->k);
+  p.m_fixed = static_cast<int>(a->n);
+  p.k = 0;
+  p.tiles_n = static_cast<int>(tiles_n);
+  p.total_tiles = p.tile_start[a->num_groups];
+  p.idesc = make_idesc(a->a_format, a->b_format, ctas, form == kWgradRowMajor, form == kWgradRowMajor);
+  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
+  if (tuning().tma_epilogue) {
+    const int rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
+    if (rc != FP8GMM_OK) return rc;
+    p.tma_store = 1;
+  }
+  return launch(p, ctas, s);
 }
 
-bool fmt_ok(int f) { return f == FP8GMM_E4M3 || f == FP8GMM_E5M2; }
+// Argument checks shared by the three entry points; *empty is set when there is nothing to do.
+int wgrad_check(const fp8gmm_wgrad_args* a, const char* name, int max_groups, bool* empty) {
+  *empty = false;
+  FP8GMM_CHECK_ARG(a != nullptr, "%s: NULL arguments", name);
+  FP8GMM_CHECK_ARG(a->num_groups >= 0 && a->num_groups <= max_groups, "%s: num_groups %d outside [0, %d]", name,
+                   a->num_groups, max_groups);
+  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "%s: bad fp8 format", name);
+  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
+                   "%s: N (%lld) and K (%lld) must be positive multiples of 16", name, (long long)a->n, (long long)a->k);
+  if (a->num_groups == 0) {
+    *empty = true;
+    return FP8GMM_OK;
+  }
+  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "%s: NULL pointer", name);
+  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "%s: NULL scale_inv pointer", name);
+  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
+                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0, "%s: operand pointers must be 16-byte aligned", name);
+  return FP8GMM_OK;
+}
+
+int wgrad_with_workspace(const fp8gmm_wgrad_args* a, void* stream, const char* name, WgradForm form) {
+  bool empty = false;
+  int rc = wgrad_check(a, name, kMaxGroups, &empty);
+  if (rc != FP8GMM_OK || empty) return rc;
+  FP8GMM_CHECK_ARG(a->workspace != nullptr && a->workspace_bytes >= fp8gmm_wgrad_workspace_bytes(a->num_groups),
+                   "%s: workspace of %zu bytes is smaller than the %zu required", name, a->workspace_bytes,
+                   fp8gmm_wgrad_workspace_bytes(a->num_groups));
+  FP8GMM_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 128 == 0, "%s: workspace must be 128-byte aligned", name);
+  std::vector<CUtensorMap> maps(static_cast<size_t>(a->num_groups) * 2);
+  return wgrad_launch(a, static_cast<cudaStream_t>(stream), name, form, static_cast<CUtensorMap*>(a->workspace), maps.data());
+}
 
 }  // namespace
 }  // namespace fp8gmm
@@ -997,12 +1097,12 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
     pad128 += (m + 127) / 128 * 128;
     pad256 += (m + 255) / 256 * 256;
   }
-  int ctas = forced_ctas();
+  int ctas = tuning().ctas;
   if (ctas == 0) ctas = (pad256 * 10 <= pad128 * 11) ? 2 : 1;
   const int tile_m = kBlockM * ctas;
   // With paired tiles a group whose last 256-row tile holds at most 128 rows would spend a whole pair tile on them
   // (every n-tile of it): such tails are left to a second launch of the single-CTA kernel, whose 128-row tile fits.
-  const bool split_tails = ctas == 2 && getenv("FP8GMM_GEMM_NO_TAIL_SPLIT") == nullptr;
+  const bool split_tails = ctas == 2 && tuning().tail_split;
   int tail_start[kMaxGroups], tail_count[kMaxGroups];
   int64_t rows = 0, tiles = 0, tail_tiles = 0;
   p.tile_start[0] = 0;
@@ -1066,7 +1166,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas, false, a->b_layout == 1);
   p.super_tiles = (a->k > kLongK ? kSuperRowsLongK : kSuperRowsShortK) / tile_m;
-  if (a->c_row_map == nullptr && a->activation != FP8GMM_ACT_GELU && tma_epilogue_enabled()) {
+  if (a->c_row_map == nullptr && a->activation != FP8GMM_ACT_GELU && tuning().tma_epilogue) {
     rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
     if (rc != FP8GMM_OK) return rc;
     p.tma_store = 1;
@@ -1099,9 +1199,13 @@ int fp8gmm_set_gemm_sm_limit(int sms) {
   return FP8GMM_OK;
 }
 
-int fp8gmm_set_gemm_profile_buffer(void* device_buffer, size_t bytes) {
-  fp8gmm::g_profile = static_cast<long long*>(device_buffer);
-  fp8gmm::g_profile_bytes = device_buffer ? bytes : 0;
+int fp8gmm_set_gemm_variant(int ctas, int tail_split, int tma_epilogue) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(ctas >= 0 && ctas <= 2, "set_gemm_variant: ctas must be 0 (automatic), 1 or 2");
+  Tuning& t = tuning();
+  t.ctas = ctas;
+  t.tail_split = tail_split != 0;
+  t.tma_epilogue = tma_epilogue != 0;
   return FP8GMM_OK;
 }
 
@@ -1110,81 +1214,8 @@ size_t fp8gmm_wgrad_workspace_bytes(int num_groups) {
 }
 
 int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
-  using namespace fp8gmm;
-  FP8GMM_CHECK_ARG(a != nullptr, "grouped_wgrad: NULL arguments");
-  FP8GMM_CHECK_ARG(a->num_groups >= 0 && a->num_groups <= kMaxGroups, "grouped_wgrad: num_groups %d outside [0, %d]",
-                   a->num_groups, kMaxGroups);
-  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_wgrad: bad fp8 format");
-  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
-                   "grouped_wgrad: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n, (long long)a->k);
-  if (a->num_groups == 0) return FP8GMM_OK;
-  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "grouped_wgrad: NULL pointer");
-  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_wgrad: NULL scale_inv pointer");
-  FP8GMM_CHECK_ARG(a->workspace != nullptr && a->workspace_bytes >= fp8gmm_wgrad_workspace_bytes(a->num_groups),
-                   "grouped_wgrad: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes,
-                   fp8gmm_wgrad_workspace_bytes(a->num_groups));
-  FP8GMM_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 128 == 0, "grouped_wgrad: workspace must be 128-byte aligned");
-  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
-                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0, "grouped_wgrad: operand pointers must be 16-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  int ctas = forced_ctas();
-  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
-  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
-  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
-  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad: problem too large");
-  std::vector<CUtensorMap> maps(static_cast<size_t>(a->num_groups) * 2);
-  memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
-  p.tile_start[0] = 0;
-  for (int g = 0; g < a->num_groups; ++g) {
-    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
-    const int64_t len = o1 - o0;
-    FP8GMM_CHECK_ARG(len >= 0 && len % 16 == 0 && o1 <= INT32_MAX - 1024,
-                     "grouped_wgrad: group %d contraction length %lld must be a non-negative multiple of 16", g,
-                     (long long)len);
-    p.row_start[g] = static_cast<int>(o0);
-    p.row_start[g + 1] = static_cast<int>(o1);
-    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
-    if (len > 0) {
-      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "grouped_wgrad: NULL operand pointer");
-      int rc = encode_map(&maps[2 * g], static_cast<const char*>(a->a_t) + o0 * a->n, static_cast<uint64_t>(a->n),
-                          static_cast<uint64_t>(len));
-      if (rc != FP8GMM_OK) return rc;
-      rc = encode_map(&maps[2 * g + 1], static_cast<const char*>(a->b_t) + o0 * a->k, static_cast<uint64_t>(a->k),
-                      static_cast<uint64_t>(len));
-      if (rc != FP8GMM_OK) return rc;
-    }
-  }
-  // Pageable source: the runtime stages the bytes before returning, so `maps` may go out of scope.
-  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(a->workspace, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
-  p.maps = static_cast<const CUtensorMap*>(a->workspace);
-  p.c = static_cast<uint16_t*>(a->c);
-  p.sa = a->a_scale_inv;
-  p.sb = a->b_scale_inv;
-  p.sa_stride = a->a_scale_inv_stride;
-  p.sb_stride = a->b_scale_inv_stride;
-  p.ldc = a->k;
-  p.status = device_status_word();
-  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_wgrad: cannot resolve the device status word");
-  p.mode = kModeWgrad;
-  p.activation = FP8GMM_ACT_NONE;
-  p.num_groups = a->num_groups;
-  p.n = static_cast<int>(a->k);
-  p.m_fixed = static_cast<int>(a->n);
-  p.k = 0;
-  p.tiles_n = static_cast<int>(tiles_n);
-  p.total_tiles = p.tile_start[a->num_groups];
-  p.idesc = make_idesc(a->a_format, a->b_format, ctas);
-  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
-  if (tma_epilogue_enabled()) {
-    const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
-    if (rc_map != FP8GMM_OK) return rc_map;
-    p.tma_store = 1;
-  }
-  return launch(p, ctas, s);
+  return fp8gmm::wgrad_with_workspace(a, stream, "grouped_wgrad", fp8gmm::kWgradTransposed);
 }
-
 
 // Weight gradients straight from the row-major FP8 activations: C_g (n x k) = dY_g^T X_g with dY_g = rows
 // [offsets[g], offsets[g+1]) of a (sum m x n) matrix and X_g the same rows of a (sum m x k) matrix.  Seen from the
@@ -1193,78 +1224,7 @@ int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* a, void* stream) {
 // activations are needed at all.  One tensor map per group and operand bounds the group's rows, and TMA zero-fills
 // the rows past its end, so group sizes need no padding either.
 int fp8gmm_grouped_wgrad_rowmajor(const fp8gmm_wgrad_args* a, void* stream) {
-  using namespace fp8gmm;
-  FP8GMM_CHECK_ARG(a != nullptr, "grouped_wgrad_rowmajor: NULL arguments");
-  FP8GMM_CHECK_ARG(a->num_groups >= 0 && a->num_groups <= kMaxGroups, "grouped_wgrad_rowmajor: num_groups %d outside [0, %d]",
-                   a->num_groups, kMaxGroups);
-  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_wgrad_rowmajor: bad fp8 format");
-  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
-                   "grouped_wgrad_rowmajor: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n, (long long)a->k);
-  if (a->num_groups == 0) return FP8GMM_OK;
-  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "grouped_wgrad_rowmajor: NULL pointer");
-  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_wgrad_rowmajor: NULL scale_inv pointer");
-  FP8GMM_CHECK_ARG(a->workspace != nullptr && a->workspace_bytes >= fp8gmm_wgrad_workspace_bytes(a->num_groups),
-                   "grouped_wgrad_rowmajor: workspace of %zu bytes is smaller than the %zu required", a->workspace_bytes,
-                   fp8gmm_wgrad_workspace_bytes(a->num_groups));
-  FP8GMM_CHECK_ARG(reinterpret_cast<uintptr_t>(a->workspace) % 128 == 0, "grouped_wgrad_rowmajor: workspace must be 128-byte aligned");
-  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
-                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0, "grouped_wgrad_rowmajor: operand pointers must be 16-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  int ctas = forced_ctas();
-  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
-  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
-  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
-  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad_rowmajor: problem too large");
-  std::vector<CUtensorMap> maps(static_cast<size_t>(a->num_groups) * 2);
-  memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
-  p.tile_start[0] = 0;
-  for (int g = 0; g < a->num_groups; ++g) {
-    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
-    const int64_t len = o1 - o0;
-    FP8GMM_CHECK_ARG(len >= 0 && o1 <= INT32_MAX - 1024, "grouped_wgrad_rowmajor: group %d has a negative or oversized row range", g);
-    p.row_start[g] = static_cast<int>(o0);
-    p.row_start[g + 1] = static_cast<int>(o1);
-    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
-    if (len > 0) {
-      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "grouped_wgrad_rowmajor: NULL operand pointer");
-      // rows x features bytes, row pitch = features: the same encoder as for K-major operands (box 128 rows x 128 bytes)
-      int rc = encode_map(&maps[2 * g], static_cast<const char*>(a->a_t) + o0 * a->n, static_cast<uint64_t>(len),
-                          static_cast<uint64_t>(a->n));
-      if (rc != FP8GMM_OK) return rc;
-      rc = encode_map(&maps[2 * g + 1], static_cast<const char*>(a->b_t) + o0 * a->k, static_cast<uint64_t>(len),
-                      static_cast<uint64_t>(a->k));
-      if (rc != FP8GMM_OK) return rc;
-    }
-  }
-  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(a->workspace, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, s));
-  p.maps = static_cast<const CUtensorMap*>(a->workspace);
-  p.c = static_cast<uint16_t*>(a->c);
-  p.sa = a->a_scale_inv;
-  p.sb = a->b_scale_inv;
-  p.sa_stride = a->a_scale_inv_stride;
-  p.sb_stride = a->b_scale_inv_stride;
-  p.ldc = a->k;
-  p.status = device_status_word();
-  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_wgrad_rowmajor: cannot resolve the device status word");
-  p.mode = kModeWgrad;
-  p.mn_major = 1;
-  p.activation = FP8GMM_ACT_NONE;
-  p.num_groups = a->num_groups;
-  p.n = static_cast<int>(a->k);
-  p.m_fixed = static_cast<int>(a->n);
-  p.k = 0;
-  p.tiles_n = static_cast<int>(tiles_n);
-  p.total_tiles = p.tile_start[a->num_groups];
-  p.idesc = make_idesc(a->a_format, a->b_format, ctas, true, true);
-  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
-  if (tma_epilogue_enabled()) {
-    const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
-    if (rc_map != FP8GMM_OK) return rc_map;
-    p.tma_store = 1;
-  }
-  return launch(p, ctas, s);
+  return fp8gmm::wgrad_with_workspace(a, stream, "grouped_wgrad_rowmajor", fp8gmm::kWgradRowMajor);
 }
 
 }  // extern "C"
@@ -1282,13 +1242,16 @@ int fp8gmm_grouped_wgrad_rowmajor(const fp8gmm_wgrad_args* a, void* stream) {
 //
 // What a caller has to know:
 //   * at most kStaticWgradMaxGroups (128) groups per call; more is rejected with FP8GMM_UNSUPPORTED;
-//   * the call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine;
+//   * the call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine, no heap;
 //   * the first call on each device looks up the array's device address (the name of a __device__ array is
 //     only a host-side handle, not an address a kernel can use) with that device current; make that first
-//     call before starting any stream capture;
+//     call before starting any stream capture.  A call on a stream that is being captured is refused with
+//     FP8GMM_UNSUPPORTED (it copies its descriptors from a stack buffer);
 //   * all calls on a device share the one array and each call overwrites all of the part it uses, so
 //     nothing from an earlier call is ever read; but two calls whose work overlaps on the GPU (different
-//     streams, no ordering between them) race on it.  Issue them on one stream or order them yourself.
+//     streams, no ordering between them) race on it.  Issue them on one stream or order them yourself;
+//   * host threads are serialised inside the call (one lock around encode, copy and launch), so two
+//     threads issuing to the same stream cannot interleave their copies and launches.
 constexpr int kStaticWgradMaxGroups = 128;
 static __device__ __align__(256) unsigned char g_static_wgrad_maps[kStaticWgradMaxGroups * 2 * sizeof(CUtensorMap)];
 
@@ -1297,12 +1260,12 @@ namespace {
 CUtensorMap* g_static_wgrad_addr[64] = {nullptr};
 std::mutex g_static_wgrad_mutex;
 
-// Device address of g_static_wgrad_maps on the current device, resolved once per device.
+// Device address of g_static_wgrad_maps on the current device, resolved once per device.  The caller holds
+// g_static_wgrad_mutex.
 int static_wgrad_scratch(CUtensorMap** out) {
   int dev = 0;
   FP8GMM_CHECK_CUDA(cudaGetDevice(&dev));
   FP8GMM_CHECK_ARG(dev >= 0 && dev < 64, "grouped_wgrad_static: device index %d out of range", dev);
-  std::lock_guard<std::mutex> lock(g_static_wgrad_mutex);
   if (g_static_wgrad_addr[dev] == nullptr) {
     void* ptr = nullptr;
     FP8GMM_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_static_wgrad_maps));
@@ -1322,76 +1285,13 @@ extern "C" int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* a, void* str
               "use fp8gmm_grouped_wgrad with a workspace", a->num_groups, kStaticWgradMaxGroups);
     return FP8GMM_UNSUPPORTED;
   }
-  FP8GMM_CHECK_ARG(a->num_groups >= 0, "grouped_wgrad_static: negative num_groups");
-  FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_wgrad_static: bad fp8 format");
-  FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
-                   "grouped_wgrad_static: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n,
-                   (long long)a->k);
-  if (a->num_groups == 0) return FP8GMM_OK;
-  FP8GMM_CHECK_ARG(a->t_offsets != nullptr && a->c != nullptr, "grouped_wgrad_static: NULL pointer");
-  FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_wgrad_static: NULL scale_inv pointer");
-  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a_t) | reinterpret_cast<uintptr_t>(a->b_t) |
-                    reinterpret_cast<uintptr_t>(a->c)) % 16 == 0,
-                   "grouped_wgrad_static: operand pointers must be 16-byte aligned");
+  bool empty = false;
+  int rc = wgrad_check(a, "grouped_wgrad_static", kStaticWgradMaxGroups, &empty);
+  if (rc != FP8GMM_OK || empty) return rc;
+  std::lock_guard<std::mutex> lock(g_static_wgrad_mutex);
   CUtensorMap* scratch = nullptr;
-  int rc = static_wgrad_scratch(&scratch);
+  rc = static_wgrad_scratch(&scratch);
   if (rc != FP8GMM_OK) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  int ctas = forced_ctas();
-  if (ctas == 0) ctas = a->n >= 256 ? 2 : 1;
-  const int64_t tiles_m = (a->n + kBlockM * ctas - 1) / (kBlockM * ctas);
-  const int64_t tiles_n = (a->k + kBlockN - 1) / kBlockN;
-  FP8GMM_CHECK_ARG(tiles_m * tiles_n * a->num_groups <= INT32_MAX / 2, "grouped_wgrad_static: problem too large");
   CUtensorMap maps[kStaticWgradMaxGroups * 2];  // host staging on the stack: no heap, no device allocation
-  memset(maps, 0, sizeof(CUtensorMap) * 2 * static_cast<size_t>(a->num_groups));
-  p.tile_start[0] = 0;
-  for (int g = 0; g < a->num_groups; ++g) {
-    const int64_t o0 = a->t_offsets[g], o1 = a->t_offsets[g + 1];
-    const int64_t len = o1 - o0;
-    FP8GMM_CHECK_ARG(len >= 0 && len % 16 == 0 && o1 <= INT32_MAX - 1024,
-                     "grouped_wgrad_static: group %d contraction length %lld must be a non-negative multiple of 16", g,
-                     (long long)len);
-    p.row_start[g] = static_cast<int>(o0);
-    p.row_start[g + 1] = static_cast<int>(o1);
-    p.tile_start[g + 1] = p.tile_start[g] + static_cast<int>(tiles_m * tiles_n);
-    if (len > 0) {
-      FP8GMM_CHECK_ARG(a->a_t && a->b_t, "grouped_wgrad_static: NULL operand pointer");
-      rc = encode_map(&maps[2 * g], static_cast<const char*>(a->a_t) + o0 * a->n, static_cast<uint64_t>(a->n),
-                      static_cast<uint64_t>(len));
-      if (rc != FP8GMM_OK) return rc;
-      rc = encode_map(&maps[2 * g + 1], static_cast<const char*>(a->b_t) + o0 * a->k, static_cast<uint64_t>(a->k),
-                      static_cast<uint64_t>(len));
-      if (rc != FP8GMM_OK) return rc;
-    }
-  }
-  // Overwrites every descriptor slot this launch reads (empty groups get zeroed slots that are never used).
-  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(scratch, maps, sizeof(CUtensorMap) * 2 * static_cast<size_t>(a->num_groups),
-                                    cudaMemcpyHostToDevice, s));
-  p.maps = scratch;
-  p.c = static_cast<uint16_t*>(a->c);
-  p.sa = a->a_scale_inv;
-  p.sb = a->b_scale_inv;
-  p.sa_stride = a->a_scale_inv_stride;
-  p.sb_stride = a->b_scale_inv_stride;
-  p.ldc = a->k;
-  p.status = device_status_word();
-  FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_wgrad_static: cannot resolve the device status word");
-  p.mode = kModeWgrad;
-  p.activation = FP8GMM_ACT_NONE;
-  p.num_groups = a->num_groups;
-  p.n = static_cast<int>(a->k);
-  p.m_fixed = static_cast<int>(a->n);
-  p.k = 0;
-  p.tiles_n = static_cast<int>(tiles_n);
-  p.total_tiles = p.tile_start[a->num_groups];
-  p.idesc = make_idesc(a->a_format, a->b_format, ctas);
-  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
-  if (tma_epilogue_enabled()) {
-    const int rc_map = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
-    if (rc_map != FP8GMM_OK) return rc_map;
-    p.tma_store = 1;
-  }
-  return launch(p, ctas, s);
+  return wgrad_launch(a, static_cast<cudaStream_t>(stream), "grouped_wgrad_static", kWgradTransposed, scratch, maps);
 }

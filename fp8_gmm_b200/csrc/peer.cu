@@ -9,8 +9,8 @@
 //   * completion is announced with one 32-bit sequence number per (receiver, sender) pair, written into the
 //     receiver's memory by a one-warp kernel that is stream-ordered after the sender's copies, and awaited
 //     by a one-warp kernel on the receiver's compute stream.  Sequence numbers only grow, so nothing is
-//     ever reset.  The wait is bounded (about two seconds): when it runs out the kernel records a code in
-//     the device status word and returns, it never hangs the GPU.
+//     ever reset.  The wait is bounded (two seconds unless fp8gmm_set_wait_limits changed it): when it runs
+//     out the kernel records a code in the device status word and returns, it never hangs the GPU.
 // A waiting kernel and the kernel that releases it always run on different GPUs.
 #include <cstring>
 
@@ -20,7 +20,6 @@ namespace fp8gmm {
 namespace {
 
 constexpr int kMaxPeers = 64;
-constexpr unsigned long long kPeerWaitLimitNs = 2000ull * 1000ull * 1000ull;
 constexpr int kStatusPeerTimeout = 0x100;
 
 struct SignalParams {
@@ -46,7 +45,7 @@ __device__ __forceinline__ unsigned long long peer_global_ns() {
 }
 
 // Lane i waits until flags[i] has reached `value` (sequence numbers compare modulo 2^32).
-__global__ void peer_wait_kernel(const uint32_t* flags, int count, uint32_t value, int* status) {
+__global__ void peer_wait_kernel(const uint32_t* flags, int count, uint32_t value, int* status, unsigned long long limit_ns) {
   const int i = threadIdx.x;
   if (i >= count) return;
   const volatile uint32_t* f = flags + i;
@@ -59,7 +58,7 @@ __global__ void peer_wait_kernel(const uint32_t* flags, int count, uint32_t valu
         return;
       }
     }
-    if (peer_global_ns() - t0 > kPeerWaitLimitNs) {
+    if (peer_global_ns() - t0 > limit_ns) {
       atomicOr(status, kStatusPeerTimeout);
       return;
     }
@@ -146,7 +145,7 @@ int fp8gmm_peer_wait(const uint32_t* flags, int count, uint32_t value, void* str
   if (count == 0) return FP8GMM_OK;
   int* status = device_status_word();
   FP8GMM_CHECK_ARG(status != nullptr, "peer_wait: cannot resolve the device status word");
-  peer_wait_kernel<<<1, kMaxPeers, 0, static_cast<cudaStream_t>(stream)>>>(flags, count, value, status);
+  peer_wait_kernel<<<1, kMaxPeers, 0, static_cast<cudaStream_t>(stream)>>>(flags, count, value, status, peer_wait_limit_ns());
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;

@@ -19,13 +19,22 @@ namespace fp8gmm {
 namespace {
 
 constexpr int kSortThreads = 1024;
+constexpr int kStatusBadExpertId = 0x200;   // an expert id outside [0, num_experts), or a row index it left unset
 
 // Number of entries equal to `expert`, one CTA per expert.
-__global__ void __launch_bounds__(kSortThreads) moe_count_kernel(const int32_t* __restrict__ ids, int64_t n, int64_t* __restrict__ counts) {
+__global__ void __launch_bounds__(kSortThreads) moe_count_kernel(const int32_t* __restrict__ ids, int64_t n, int num_experts,
+                                                                 int64_t* __restrict__ counts, int* __restrict__ status) {
   __shared__ int warp_sums[kSortThreads / 32];
   const int expert = blockIdx.x;
   int local = 0;
-  for (int64_t i = threadIdx.x; i < n; i += kSortThreads) local += ids[i] == expert;
+  bool bad = false;
+  for (int64_t i = threadIdx.x; i < n; i += kSortThreads) {
+    const int32_t id = ids[i];
+    local += id == expert;
+    bad |= id < 0 || id >= num_experts;
+  }
+  // Ids outside the range match no CTA, so their rows would stay unsorted: report them (the first CTA looks).
+  if (expert == 0 && __syncthreads_or(bad) && threadIdx.x == 0) atomicOr(status, kStatusBadExpertId);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xFFFFFFFFu, local, o);
   if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = local;
@@ -107,12 +116,16 @@ __device__ __forceinline__ uint16_t float_to_bf16(float f) {
 template <bool kVec>
 __global__ void __launch_bounds__(256) moe_gather_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ indices,
                                                          const float* __restrict__ weights, int top_k, int64_t rows, int64_t cols,
-                                                         uint16_t* __restrict__ out) {
+                                                         uint16_t* __restrict__ out, int* __restrict__ status) {
   const int64_t per_row = kVec ? cols / 8 : cols;
   const int64_t total = rows * per_row;
   for (int64_t id = blockIdx.x * 256ll + threadIdx.x; id < total; id += 256ll * gridDim.x) {
     const int64_t r = id / per_row, c = id - r * per_row;
     const int32_t slot = indices[r];
+    if (slot < 0 || slot >= rows) {   // not a permutation entry (the sort saw an invalid expert id): skip, report
+      if (c == 0) atomicOr(status, kStatusBadExpertId);
+      continue;
+    }
     const int64_t src = slot / top_k;
     if (kVec) {
       uint4 v = __ldg(reinterpret_cast<const uint4*>(x + src * cols) + c);
@@ -137,9 +150,10 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const uint16_t* __restr
 template <bool kVec>
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ inverse,
                                                           const float* __restrict__ weights, int top_k, int64_t tokens, int64_t cols,
-                                                          uint16_t* __restrict__ out) {
+                                                          uint16_t* __restrict__ out, int* __restrict__ status) {
   const int64_t per_row = kVec ? cols / 8 : cols;
   const int64_t total = tokens * per_row;
+  const int64_t n_rows = tokens * top_k;
   for (int64_t id = blockIdx.x * 256ll + threadIdx.x; id < total; id += 256ll * gridDim.x) {
     const int64_t t = id / per_row, c = id - t * per_row;
     if (kVec) {
@@ -149,8 +163,13 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const uint16_t* __rest
       for (int k = 0; k < top_k; ++k) {
         const int64_t p = t * top_k + k;
         const float w = weights != nullptr ? weights[p] : 1.f;
+        const int64_t src = inverse[p];
+        if (src < 0 || src >= n_rows) {   // position the sort never placed: contributes nothing, reported
+          if (c == 0) atomicOr(status, kStatusBadExpertId);
+          continue;
+        }
         float f[8];
-        unpack8(ld_stream16(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(inverse[p]) * cols) + c), f);
+        unpack8(ld_stream16(reinterpret_cast<const uint4*>(x + src * cols) + c), f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, f[j], acc[j]);
       }
@@ -160,7 +179,12 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const uint16_t* __rest
       for (int k = 0; k < top_k; ++k) {
         const int64_t p = t * top_k + k;
         const float w = weights != nullptr ? weights[p] : 1.f;
-        acc = fmaf(w, bf16_to_float(x[static_cast<int64_t>(inverse[p]) * cols + c]), acc);
+        const int64_t src = inverse[p];
+        if (src < 0 || src >= n_rows) {
+          if (c == 0) atomicOr(status, kStatusBadExpertId);
+          continue;
+        }
+        acc = fmaf(w, bf16_to_float(x[src * cols + c]), acc);
       }
       out[t * cols + c] = float_to_bf16(acc);
     }
@@ -170,12 +194,20 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const uint16_t* __rest
 // d_weights[p] = <grad[p / top_k], x[inverse[p]]>, one warp per (token, slot) position.
 __global__ void __launch_bounds__(256) moe_rowdot_kernel(const uint16_t* __restrict__ grad, const uint16_t* __restrict__ x,
                                                          const int32_t* __restrict__ inverse, int top_k, int64_t n, int64_t cols,
-                                                         float* __restrict__ d_weights) {
+                                                         float* __restrict__ d_weights, int* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (256ll * gridDim.x) >> 5;
   for (int64_t p = (blockIdx.x * 256ll + threadIdx.x) >> 5; p < n; p += warps) {
+    const int64_t src = inverse[p];
+    if (src < 0 || src >= n) {
+      if (lane == 0) {
+        atomicOr(status, kStatusBadExpertId);
+        d_weights[p] = 0.f;
+      }
+      continue;
+    }
     const uint16_t* g = grad + (p / top_k) * cols;
-    const uint16_t* v = x + static_cast<int64_t>(inverse[p]) * cols;
+    const uint16_t* v = x + src * cols;
     float acc = 0.f;
     if (cols % 8 == 0 && (reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(v)) % 16 == 0) {
       for (int64_t c = lane; c < cols / 8; c += 32) {
@@ -191,6 +223,89 @@ __global__ void __launch_bounds__(256) moe_rowdot_kernel(const uint16_t* __restr
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
     if (lane == 0) d_weights[p] = acc;
+  }
+}
+
+// Router: softmax over the expert logits in fp32, then the top_k largest probabilities (descending; equal values
+// keep the lower expert id first), optionally renormalised to sum to one (reference fp8_gmm/example.py:14-23).
+// One warp per token; lane l holds experts l, l + 32, ...
+constexpr int kTopkMaxPerLane = 32;   // up to 1024 experts
+template <typename T>
+__device__ __forceinline__ float logit_to_float(T v);
+template <>
+__device__ __forceinline__ float logit_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float logit_to_float<uint16_t>(uint16_t v) { return bf16_to_float(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_topk_kernel(const T* __restrict__ logits, int64_t tokens, int num_experts, int top_k,
+                                                       int renorm, float* __restrict__ probs, float* __restrict__ weights,
+                                                       int32_t* __restrict__ experts) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (256ll * gridDim.x) >> 5;
+  for (int64_t t = (blockIdx.x * 256ll + threadIdx.x) >> 5; t < tokens; t += warps) {
+    const T* row = logits + t * num_experts;
+    float v[kTopkMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kTopkMaxPerLane; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = e < num_experts ? logit_to_float<T>(row[e]) : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kTopkMaxPerLane; ++i) {
+      v[i] = lane + 32 * i < num_experts ? expf(v[i] - mx) : 0.f;
+      sum += v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+#pragma unroll
+    for (int i = 0; i < kTopkMaxPerLane; ++i) {
+      v[i] = __fdiv_rn(v[i], sum);
+      const int e = lane + 32 * i;
+      if (probs != nullptr && e < num_experts) probs[t * num_experts + e] = v[i];
+    }
+    float picked_sum = 0.f;
+    float my_weight = 0.f;   // lane r keeps the r-th pick until the renormalisation is known
+    int my_expert = 0;
+    for (int r = 0; r < top_k; ++r) {
+      float best = -1.f;
+      int best_e = INT32_MAX;
+#pragma unroll
+      for (int i = 0; i < kTopkMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        if (e < num_experts && v[i] > best) best = v[i], best_e = e;   // ascending e: the first maximum wins
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) best = ob, best_e = oe;
+      }
+      if ((best_e & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < kTopkMaxPerLane; ++i)
+          if (i == (best_e >> 5)) v[i] = -2.f;   // taken
+      }
+      picked_sum += best;
+      if (lane == (r & 31)) my_weight = best, my_expert = best_e;
+      if ((r & 31) == 31 || r == top_k - 1) {
+        // top_k may exceed 32: flush this batch of picks (renormalisation then needs a second pass, below)
+        const int base = r & ~31;
+        if (lane <= (r & 31)) {
+          weights[t * top_k + base + lane] = my_weight;
+          experts[t * top_k + base + lane] = my_expert;
+        }
+      }
+    }
+    if (renorm) {
+      __syncwarp();
+      for (int r = lane; r < top_k; r += 32) weights[t * top_k + r] = __fdiv_rn(weights[t * top_k + r], picked_sum);
+    }
   }
 }
 
@@ -212,13 +327,41 @@ int fp8gmm_moe_sort(const int32_t* expert_ids, int64_t n, int num_experts, int32
   FP8GMM_CHECK_ARG(bins != nullptr && tokens_per_expert != nullptr, "moe_sort: NULL histogram output");
   FP8GMM_CHECK_ARG(n == 0 || (expert_ids && indices && bin_ids && inverse), "moe_sort: NULL pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  moe_count_kernel<<<num_experts, kSortThreads, 0, s>>>(expert_ids, n, tokens_per_expert);
+  int* status = device_status_word();
+  FP8GMM_CHECK_ARG(status != nullptr, "moe_sort: cannot resolve the device status word");
+  if (n > 0) {
+    // positions that no CTA places (ids out of range) keep -1, which the gather / scatter kernels recognise
+    FP8GMM_CHECK_CUDA(cudaMemsetAsync(indices, 0xFF, static_cast<size_t>(n) * sizeof(int32_t), s));
+    FP8GMM_CHECK_CUDA(cudaMemsetAsync(inverse, 0xFF, static_cast<size_t>(n) * sizeof(int32_t), s));
+  }
+  moe_count_kernel<<<num_experts, kSortThreads, 0, s>>>(expert_ids, n, num_experts, tokens_per_expert, status);
   moe_bins_kernel<<<1, 32, 0, s>>>(tokens_per_expert, num_experts, bins);
   if (n > 0) moe_place_kernel<<<num_experts, kSortThreads, 0, s>>>(expert_ids, n, bins, indices, bin_ids, inverse);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   count_launch();
   if (n > 0) count_launch();
+  return FP8GMM_OK;
+}
+
+int fp8gmm_moe_topk(const void* logits, int logits_are_bf16, int64_t tokens, int num_experts, int top_k, int renormalize,
+                    float* probs, float* weights, int32_t* experts, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(tokens >= 0 && num_experts > 0 && num_experts <= 32 * kTopkMaxPerLane, "moe_topk: num_experts must be in [1, %d]",
+                   32 * kTopkMaxPerLane);
+  FP8GMM_CHECK_ARG(top_k > 0 && top_k <= num_experts, "moe_topk: top_k must be in [1, num_experts]");
+  if (tokens == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(logits && weights && experts, "moe_topk: NULL pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = row_grid(tokens * 32);
+  if (logits_are_bf16)
+    moe_topk_kernel<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(logits), tokens, num_experts, top_k, renormalize,
+                                                   probs, weights, experts);
+  else
+    moe_topk_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(logits), tokens, num_experts, top_k, renormalize, probs,
+                                                weights, experts);
+  FP8GMM_CHECK_CUDA(cudaGetLastError());
+  count_launch();
   return FP8GMM_OK;
 }
 
@@ -229,13 +372,15 @@ int fp8gmm_moe_gather(const void* x, const int32_t* indices, const float* weight
   if (rows == 0 || cols == 0) return FP8GMM_OK;
   FP8GMM_CHECK_ARG(x && indices && out, "moe_gather: NULL pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = device_status_word();
+  FP8GMM_CHECK_ARG(status != nullptr, "moe_gather: cannot resolve the device status word");
   const bool vec = cols % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
   if (vec)
     moe_gather_kernel<true><<<row_grid(rows * (cols / 8)), 256, 0, s>>>(static_cast<const uint16_t*>(x), indices, weights, top_k,
-                                                                       rows, cols, static_cast<uint16_t*>(out));
+                                                                       rows, cols, static_cast<uint16_t*>(out), status);
   else
     moe_gather_kernel<false><<<row_grid(rows * cols), 256, 0, s>>>(static_cast<const uint16_t*>(x), indices, weights, top_k, rows,
-                                                                  cols, static_cast<uint16_t*>(out));
+                                                                  cols, static_cast<uint16_t*>(out), status);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;
@@ -248,13 +393,15 @@ int fp8gmm_moe_scatter(const void* x, const int32_t* inverse, const float* weigh
   if (tokens == 0 || cols == 0) return FP8GMM_OK;
   FP8GMM_CHECK_ARG(x && inverse && out, "moe_scatter: NULL pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = device_status_word();
+  FP8GMM_CHECK_ARG(status != nullptr, "moe_scatter: cannot resolve the device status word");
   const bool vec = cols % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
   if (vec)
     moe_scatter_kernel<true><<<row_grid(tokens * (cols / 8)), 256, 0, s>>>(static_cast<const uint16_t*>(x), inverse, weights, top_k,
-                                                                          tokens, cols, static_cast<uint16_t*>(out));
+                                                                          tokens, cols, static_cast<uint16_t*>(out), status);
   else
     moe_scatter_kernel<false><<<row_grid(tokens * cols), 256, 0, s>>>(static_cast<const uint16_t*>(x), inverse, weights, top_k,
-                                                                     tokens, cols, static_cast<uint16_t*>(out));
+                                                                     tokens, cols, static_cast<uint16_t*>(out), status);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;
@@ -266,8 +413,10 @@ int fp8gmm_moe_rowdot(const void* grad, const void* x, const int32_t* inverse, i
   FP8GMM_CHECK_ARG(top_k > 0 && n >= 0 && cols >= 0, "moe_rowdot: bad sizes");
   if (n == 0) return FP8GMM_OK;
   FP8GMM_CHECK_ARG(grad && x && inverse && d_weights, "moe_rowdot: NULL pointer");
+  int* status = device_status_word();
+  FP8GMM_CHECK_ARG(status != nullptr, "moe_rowdot: cannot resolve the device status word");
   moe_rowdot_kernel<<<row_grid(n * 32), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(grad), static_cast<const uint16_t*>(x), inverse, top_k, n, cols, d_weights);
+      static_cast<const uint16_t*>(grad), static_cast<const uint16_t*>(x), inverse, top_k, n, cols, d_weights, status);
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;

@@ -16,6 +16,10 @@ int g_sm_count[kMaxDevices] = {0};
 int* g_status_addr[kMaxDevices] = {nullptr};
 std::mutex g_mutex;
 std::atomic<uint64_t> g_launches{0};
+// Bounded waits: a GEMM role gives up on an mbarrier after the first limit, fp8gmm_peer_wait on its sequence
+// numbers after the second (defaults 1 s and 2 s; fp8gmm_set_wait_limits).
+std::atomic<unsigned long long> g_gemm_wait_ns{1000ull * 1000ull * 1000ull};
+std::atomic<unsigned long long> g_peer_wait_ns{2000ull * 1000ull * 1000ull};
 
 // One status word per device that loads the library (a __device__ variable is instantiated per device).
 __device__ int g_device_status = 0;
@@ -40,6 +44,8 @@ static int current_device() {
 }
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+unsigned long long gemm_wait_limit_ns() { return g_gemm_wait_ns.load(std::memory_order_relaxed); }
+unsigned long long peer_wait_limit_ns() { return g_peer_wait_ns.load(std::memory_order_relaxed); }
 
 int sm_count() {
   const int dev = current_device();
@@ -121,6 +127,24 @@ int fp8gmm_device_status(void* stream) {
     fp8gmm::set_error("a kernel gave up on a bounded wait (code 0x%x)", host);
     return FP8GMM_DEVICE_TIMEOUT;
   }
+  return FP8GMM_OK;
+}
+
+int fp8gmm_device_status_async(int* host_word, void* stream) {
+  FP8GMM_CHECK_ARG(host_word != nullptr, "device_status_async: NULL destination");
+  int* word = fp8gmm::device_status_word();
+  if (word == nullptr) {
+    fp8gmm::set_error("cannot resolve the device status word");
+    return FP8GMM_CUDA_ERROR;
+  }
+  FP8GMM_CHECK_CUDA(cudaMemcpyAsync(host_word, word, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  return FP8GMM_OK;
+}
+
+int fp8gmm_set_wait_limits(int64_t gemm_wait_ns, int64_t peer_wait_ns) {
+  FP8GMM_CHECK_ARG(gemm_wait_ns >= 0 && peer_wait_ns >= 0, "set_wait_limits: limits must not be negative (0 keeps the current one)");
+  if (gemm_wait_ns > 0) fp8gmm::g_gemm_wait_ns.store(static_cast<unsigned long long>(gemm_wait_ns), std::memory_order_relaxed);
+  if (peer_wait_ns > 0) fp8gmm::g_peer_wait_ns.store(static_cast<unsigned long long>(peer_wait_ns), std::memory_order_relaxed);
   return FP8GMM_OK;
 }
 

@@ -17,6 +17,7 @@ on one device, reference fp8_gmm/example.py:52-59,85-92); numerics per expert ar
 
 The plan arithmetic (PeerPlan) is pure host code and is tested on CPU by simulating the copies.
 """
+import copy
 import weakref
 
 import numpy as np
@@ -202,20 +203,48 @@ def resolve_result_buffers(picks, buffers_before):
 
 class EpContext:
     """Per (device, group) transport state shared by all ExpertParallelMlp modules: the channel (side stream and
-    sequence numbers), the receive buffer for dispatched rows and the pool of result buffers."""
+    sequence numbers), the receive buffer for dispatched rows and the pool of result buffers.
+
+    Creating it is collective: every rank of ``group`` exchanges IPC handles, and with ``group=None`` and no
+    ``host_group`` a gloo group over ALL ranks of the job is created.  Call ``EpContext.setup`` on every rank at a
+    point all of them reach (the first forward does it implicitly, which is only safe when every rank of the group
+    -- of the whole job for ``group=None`` -- runs that forward).  In a job where only some ranks hold an
+    ExpertParallelMlp, pass the expert-parallel ``group`` and a gloo ``host_group`` over the same ranks.
+    ``close()`` (collective as well) unmaps and frees the buffers."""
 
     _instances = {}
 
     @classmethod
-    def get(cls, device, group=None):
+    def setup(cls, device, group=None, host_group=None):
         key = (device.index, id(group))
         if key not in cls._instances:
-            cls._instances[key] = cls(device, group)
+            cls._instances[key] = cls(device, group, host_group)
         return cls._instances[key]
 
-    def __init__(self, device, group):
+    get = setup
+
+    def close(self):
+        """Frees this context's peer buffers.  Collective: every rank calls it, with no exchange in flight."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for buf in [self.recv, self._amax_stage] + self.pool.buffers:
+            if buf is not None:
+                buf.close()
+        for ch in (self.channel, self.channel_back, self.ready):
+            ch.close()
+        self.recv = self._amax_stage = self._amax_view = None
+        self.pool.buffers, self.pool.free = [], []
+        self._instances.pop((self.device.index, id(self.group)), None)
+
+    def __init__(self, device, group, host_group=None):
         self.device, self.group = device, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        # Bounded waits that ran out (a peer more than fp8gmm_set_wait_limits late) are noticed one step later,
+        # without a synchronisation: the step ends with an asynchronous copy of the device status word, the next
+        # step begins by looking at it and refuses to go on with rows that never arrived.
+        self.status = backend.StatusWatch()
+        self.failed = False
+        self._last_plan = None
         # two channels = two side streams: dispatch and combine copies run on different copy engines at the same time
         # (four copy lanes each: blocks of 8-16 MiB moved 8-9 % faster than over one lane in a 4-GPU all-to-all pattern)
         self.channel = PeerChannel(device, group, copy_streams=4)          # dispatch rounds
@@ -225,7 +254,7 @@ class EpContext:
         # of the GPU and a late host on one rank does not stall the others' GPUs.  A sub-group keeps the device gather
         # (creating a gloo group is collective over all ranks of the job).
         self.ready = PeerChannel(device, group)
-        self.host_group = dist.new_group(backend="gloo") if group is None else None
+        self.host_group = host_group if host_group is not None else (dist.new_group(backend="gloo") if group is None else None)
         self.pool = _Pool(device, group)
         self.recv = None
         self._amax_stage = None
@@ -269,7 +298,13 @@ class EpContext:
         free_seq = self.ready.push_arrays(np.empty(0, dtype=PeerChannel._BLOCK))
         for ch in (self.channel, self.channel_back):
             check(lib.fp8gmm_peer_wait(self.ready.flags.local, self.world, free_seq, ch.stream.cuda_stream), "peer_wait")
-        plan = PeerPlan(gathered[:, :E].contiguous(), self.rank, num_chunks)
+        counts = gathered[:, :E].contiguous()
+        last = self._last_plan
+        if last is not None and last[1] == repr(num_chunks) and torch.equal(last[0].counts, counts):
+            plan = copy.copy(last[0])   # same routing as the step before: offsets and copy lists are shared, buffer ids are not
+        else:
+            plan = PeerPlan(counts, self.rank, num_chunks)
+            self._last_plan = (plan, repr(num_chunks))
         # collective growth: everybody allocates as many new result buffers as the neediest rank asked for
         picks = gathered[:, E:].tolist()
         n_before = len(pool.buffers)
@@ -464,6 +499,8 @@ class _PeerEpMlp(torch.autograd.Function):
             ctx.cumsums, ctx.offs, ctx.sizes_cpu = cumsums, offs, sizes_cpu
             ctx.fc1_shape, ctx.fc2_shape = fc1_weight.shape, fc2_weight.shape
             ctx.need_wgrad, ctx.need_dgrad = need_wgrad, need_dgrad
+        else:
+            ectx.status.record()
         return out
 
     @staticmethod
@@ -574,13 +611,23 @@ class _PeerEpMlp(torch.autograd.Function):
                 backend.grouped_wgrad_rowmajor(grad_pre_fp8[r0:r1], input_t_fp8[r0:r1], _rel(cumsums, j0, j1), dpre_si,
                                                ms(_T.kForwardInputGroup1, _M.kScaleInv, j0), c=grad_fc1[j0:j1])
         ch_back.wait(last)
+        ectx.status.record()
         return gi, grad_fc1, grad_fc2, None
 
 
 def forward(module, input, group_sizes, is_first_microbatch, num_chunks):
     """ExpertParallelMlp.forward over the peer-memory transport."""
     mlp = module.mlp
-    ectx = EpContext.get(input.device, module.group)
+    ectx = EpContext.setup(input.device, module.group)
+    if not ectx.failed:
+        try:
+            ectx.status.check()
+        except RuntimeError:
+            ectx.failed = True     # no further pushes into buffers whose state is unknown
+            raise
+    if ectx.failed:
+        raise RuntimeError("fp8_gmm_b200: the expert-parallel exchange was abandoned after a device-side timeout; "
+                           "rebuild the process group and the modules")
     grad_on = torch.is_grad_enabled()
     want_gi = grad_on and input.requires_grad
     mlp.get_fp8_weights_scratchpad(is_first_microbatch)

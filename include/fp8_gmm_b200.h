@@ -54,6 +54,22 @@ const char* fp8gmm_last_error(void);
 int fp8gmm_device_status(void* stream);
 
 /*
+ * Enqueues on `stream` a copy of the device-side status word into `host_word` (page-locked host memory owned by
+ * the caller) without synchronising and without clearing the word.  A training loop calls it at the end of a step
+ * and looks at `*host_word` when it starts the next one: non-zero means a bounded wait ran out in some earlier
+ * launch, whose outputs are then undefined.
+ */
+int fp8gmm_device_status_async(int* host_word, void* stream);
+
+/*
+ * Limits of the bounded waits, in nanoseconds, process-wide, for launches made from now on; 0 keeps the current
+ * value.  `gemm_wait_ns`: how long a role of the grouped-GEMM kernel waits on an mbarrier (default 1 s).
+ * `peer_wait_ns`: how long fp8gmm_peer_wait spins on its sequence numbers (default 2 s) -- raise it where a rank
+ * may legitimately be seconds late (a checkpoint write, a stalled data loader).
+ */
+int fp8gmm_set_wait_limits(int64_t gemm_wait_ns, int64_t peer_wait_ns);
+
+/*
  * Number of kernels this library has launched in this process so far (all devices, all threads).
  * Benchmarks difference it around a timed region to state how much of the work ran in these kernels.
  */
@@ -266,6 +282,16 @@ typedef struct {
 } fp8gmm_wgrad_args;
 
 size_t fp8gmm_wgrad_workspace_bytes(int num_groups);
+int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* args, void* stream);
+
+/*
+ * Process-wide switches of the grouped-GEMM launches, for tests and experiments; no counterpart in the reference.
+ * ctas: 0 = choose per call (default), 1 = single-CTA 128 x 256 tiles, 2 = CTA-pair 256 x 256 tiles.
+ * tail_split (default 1): with pair tiles, group tails of at most 128 rows go to a second launch on 128-row tiles.
+ * tma_epilogue (default 1): full 32-row slabs of a tile leave through shared memory and TMA stores.
+ * All variants compute every output element with the same arithmetic, so results are bit-identical.
+ */
+int fp8gmm_set_gemm_variant(int ctas, int tail_split, int tma_epilogue);
 
 /*
  * fp8gmm_grouped_wgrad for callers that cannot allocate device memory.  It has no counterpart in the
@@ -278,9 +304,13 @@ size_t fp8gmm_wgrad_workspace_bytes(int num_groups);
  *   - at most 128 groups per call; more returns FP8GMM_UNSUPPORTED with a message;
  *   - the call performs no cudaMalloc / cudaFree and calls no allocating library routine;
  *   - the first call on each device resolves the array's device address (with that device current): make
- *     that first call before any stream capture begins;
+ *     that first call before any stream capture begins.  The call itself copies its descriptors from a
+ *     buffer on the host stack, so it returns FP8GMM_UNSUPPORTED on a stream that is being captured (so do
+ *     fp8gmm_grouped_wgrad and fp8gmm_grouped_wgrad_rowmajor, whose host staging is as short-lived);
  *   - all calls on one device share the array; each call rewrites every slot it reads, but calls whose GPU
- *     work may overlap (different streams without ordering) race on it -- keep them on one stream.
+ *     work may overlap (different streams without ordering) race on it -- keep them on one stream;
+ *   - host threads are serialised inside the call, so concurrent callers cannot interleave each other's
+ *     descriptor copies and launches.
  */
 int fp8gmm_grouped_wgrad_static(const fp8gmm_wgrad_args* args, void* stream);
 
@@ -302,19 +332,6 @@ int fp8gmm_set_gemm_sm_limit(int sms);
  * fp8gmm_grouped_wgrad.
  */
 int fp8gmm_grouped_wgrad_rowmajor(const fp8gmm_wgrad_args* args, void* stream);
-
-/*
- * Profiling aid with no counterpart in the reference: while a device buffer of at least
- * 8 * sizeof(int64) * (number of CTAs launched, at most 148) bytes is installed, every grouped-GEMM CTA
- * writes its stall counters in SM clock cycles to buffer[cta*8 + i]:
- *   0 producer waiting for a free shared-memory stage      1 MMA warp waiting for operands to land
- *   2 MMA warp waiting for a free TMEM accumulator         3 MMA warp total
- *   4 epilogue waiting for an accumulator                  5 epilogue busy (TMEM read, math, stores)
- *   6 MMA warp inside the MMA / commit instructions        7 MMA warp total in nanoseconds (slot 3 / slot 7 = SM GHz)
- * NULL removes it.  Process-wide; meant for one launch at a time under a benchmark, not for production.
- */
-int fp8gmm_set_gemm_profile_buffer(void* device_buffer, size_t bytes);
-int fp8gmm_grouped_wgrad(const fp8gmm_wgrad_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Delayed-scaling recipe update (the Transformer Engine hook the reference relies on through
@@ -386,8 +403,8 @@ int fp8gmm_peer_copy_blocks(const fp8gmm_copy_block* blocks, int count, void* st
 int fp8gmm_peer_signal(uint32_t* const* flags, int count, uint32_t value, void* stream);
 
 /* One-warp kernel on `stream`: returns once all of flags[0..count) (device array in local memory, count <= 64) have
- * reached `value` (compared modulo 2^32).  The wait is bounded (about two seconds); when it runs out the kernel
- * sets a bit in the device status word (see fp8gmm_device_status) and returns. */
+ * reached `value` (compared modulo 2^32).  The wait is bounded (two seconds unless fp8gmm_set_wait_limits changed
+ * it); when it runs out the kernel sets a bit in the device status word (see fp8gmm_device_status) and returns. */
 int fp8gmm_peer_wait(const uint32_t* flags, int count, uint32_t value, void* stream);
 
 #ifdef __cplusplus

@@ -57,23 +57,30 @@ def test_grouped_gemm_matches_oracle(cuda, sizes, k, n, a_dtype):
 
 @pytest.mark.parametrize("sizes,k,n,a_dtype", [([300, 0, 129, 256, 511, 5, 1025], 272, 512, E4), ([4122, 98, 640], 128, 256, E5)])
 @pytest.mark.parametrize("ctas", ["1", "2"])
-def test_forced_tile_shapes_and_tail_split(cuda, monkeypatch, sizes, k, n, a_dtype, ctas):
+def test_forced_tile_shapes_and_tail_split(cuda, sizes, k, n, a_dtype, ctas):
     """Both tile shapes forced on ragged groups.  With pair tiles (256 rows), tails of at most 128 rows leave the pair
     launch for a second launch on 128-row tiles: groups of 300, 129, 5, 1025 rows exercise that split, 511 and 256
     do not, and the results must equal the single-CTA kernel's bit for bit (same per-element arithmetic)."""
     from fp8_gmm_b200 import backend
 
-    monkeypatch.setenv("FP8GMM_GEMM_CTAS", ctas)
     a, b, sa, sb = _operands(sizes, k, n, a_dtype, seed=7)
     c = torch.full((sum(sizes), n), float("nan"), dtype=torch.bfloat16, device=cuda)
-    got = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda), c=c)
-    backend.device_status()
-    assert not torch.isnan(got.float()).any()
-    ref = O.grouped_gemm(a, b, sizes, sa, sb, out_fp32=True)
-    assert O.rel_frobenius(got.cpu(), ref) <= TOL
-    monkeypatch.setenv("FP8GMM_GEMM_CTAS", "1")
-    one = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda))
-    assert torch.equal(got, one)
+    try:
+        backend.set_gemm_variant(ctas=int(ctas))
+        got = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda), c=c)
+        backend.device_status()
+        assert not torch.isnan(got.float()).any()
+        ref = O.grouped_gemm(a, b, sizes, sa, sb, out_fp32=True)
+        assert O.rel_frobenius(got.cpu(), ref) <= TOL
+        backend.set_gemm_variant(ctas=1)
+        one = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda))
+        assert torch.equal(got, one)
+        # the per-thread-store epilogue and the unsplit pair launch compute the same bits
+        backend.set_gemm_variant(ctas=int(ctas), tail_split=False, tma_epilogue=False)
+        plain = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda))
+        assert torch.equal(got, plain)
+    finally:
+        backend.set_gemm_variant()
 
 
 def test_cublas_fp8_gemm_single_group(cuda):

@@ -4,9 +4,9 @@ Some hosts of this library cannot give it a device workspace and cannot allocate
 that has reserved the whole GPU for its own pool, a runtime that forbids plug-ins to allocate once it is
 running).  For them the weight-gradient GEMM exists in a form that keeps its per-group TMA descriptors in
 a fixed array inside the library.  This test calls that entry point directly through the C ABI, twice in a
-row with different group layouts (the second call must not be disturbed by what the first left in the
-shared array), and requires the same bits as the workspace-taking entry point produces, which the other
-GPU tests hold to <= 4e-3 relative Frobenius error against the CPU oracle.  The size limit is checked too.
+row with different group layouts (a call must not be disturbed by what the one before left in the shared
+array, also when it uses fewer slots), and requires the same bits as the workspace-taking entry point produces
+and <= 4e-3 relative Frobenius error against the CPU oracle.  The size limit is checked too.
 
 The file name sorts last on purpose: a run that stops at the first failure has then run everything else.
 """
@@ -48,10 +48,23 @@ def _call_static(lib_mod, a_t, b_t, offs, n, k, sa, sb, c):
     return lib_mod.lib.fp8gmm_grouped_wgrad_static(ctypes.byref(args), torch.cuda.current_stream().cuda_stream)
 
 
-def test_static_wgrad_matches_workspace_wgrad_twice_in_a_row(cuda):
+def _oracle_wgrad(a_t, b_t, offs, n, k, sa, sb):
+    """The CPU oracle on the same padded-transposed blocks."""
+    from oracle import oracle as O
+
+    a8, b8 = a_t.cpu().view(torch.uint8), b_t.cpu().view(torch.uint8)
+    G = len(offs) - 1
+    blocks_a = [a8[offs[g] * n:offs[g + 1] * n].reshape(n, offs[g + 1] - offs[g]).view(E5) for g in range(G)]
+    blocks_b = [b8[offs[g] * k:offs[g + 1] * k].reshape(k, offs[g + 1] - offs[g]).view(E4) for g in range(G)]
+    return O, O.grouped_wgrad(blocks_a, blocks_b, sa.cpu(), sb.cpu())
+
+
+def test_static_wgrad_matches_workspace_wgrad_and_the_oracle_on_calls_in_a_row(cuda):
     from fp8_gmm_b200 import _lib, backend
 
-    cases = [([128, 0, 37, 300, 16, 1], 272, 144, 11), ([64, 200, 5], 512, 256, 12)]
+    # three calls back to back; the third has fewer groups than the one before, so descriptor slots of the shared
+    # array that the second call filled are stale during the third and must not be read
+    cases = [([128, 0, 37, 300, 16, 1], 272, 144, 11), ([64, 200, 5], 512, 256, 12), ([48, 7], 512, 256, 13)]
     for sizes, n, k, seed in cases:
         offs, a_t, b_t, sa, sb = _operands(sizes, n, k, seed, cuda)
         G = len(sizes)
@@ -61,6 +74,8 @@ def test_static_wgrad_matches_workspace_wgrad_twice_in_a_row(cuda):
         assert rc == 0, _lib.lib.fp8gmm_last_error()
         backend.device_status()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        O, ref = _oracle_wgrad(a_t, b_t, offs, n, k, sa, sb)
+        assert O.rel_frobenius(got.cpu(), ref) <= 4e-3
         for g, m in enumerate(sizes):
             if m == 0:
                 assert (got[g] == 0).all()
