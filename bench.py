@@ -13,7 +13,15 @@ backward of GroupedMlp over one routed batch.  Prints ONE JSON line on rank 0:
                  launch / mean launch duration from CUDA events recorded around each launch inside the timed
                  region, against 2 x the measured dense bf16 rate (dense FP8 is twice bf16 on this part);
 * ``cpu_baseline`` the CPU oracle (torch per-group float8-emulated matmuls + CPU quantise/transposes)
-                 timed on the host cores on a bounded sample of the same workload.
+                 timed on the host cores on a bounded sample of the same workload;
+* ``pad``        (N = 1) the HBM-bound kernel families on the pad / cast microbenchmark (256 groups, rows ~ U[0, 4096],
+                 K = 7168, bf16 ~ N(0, 3) with 0.1 % outliers x 100): algorithmic bytes, GB/s, fraction of the measured
+                 copy bandwidth and of 8 TB/s for each op;
+* ``library_gemm`` (N = 1) this package's grouped GEMM beside the per-group ``torch._scaled_mm`` loop (cuBLASLt) on the
+                 six GEMM shapes of the step: a comparison leg, the library is never on the product path;
+* ``fine_grained`` (N = 1) the fine-grained MoE step (64 experts, hidden 2048, ffn 1408, 49152 rows, Zipf loads);
+* ``ep``         (N > 1) efficiency against the exchange-free local step, exposed waits, host time per rank, and
+                 ``check``: one extra step compared bit for bit with the NCCL all-to-all transport from the same state.
 
 ``--impl reference`` times that CPU path alone (the reference has no CPU or sm_100 implementation of
 its own: its GEMM is Hopper-only CUTLASS and its other GEMM path needs Transformer Engine, so the
@@ -41,9 +49,17 @@ import torch  # noqa: E402
 
 METRIC = "grouped_mlp_fwd_bwd_fp8_tflops"
 NOMINAL_FP8_TFLOPS = 4500.0
-# DRAM bytes (read + write) per GEMM launch, averaged over the six launches of one Mixtral-shaped step,
-# from the ncu capture summarised in profiles/ (None until a capture exists).
-GEMM_DRAM_BYTES_PER_LAUNCH = 2.850e9  # 17.10 GB over the six launches (profiles/grouped_gemm_mixtral_step_dram_traffic.md)
+# DRAM bytes (read + write) per GEMM launch, averaged over the six launches of one Mixtral-shaped step, from a
+# one-pass ncu capture of the six full-size launches (dram__bytes_read.sum + dram__bytes_write.sum: 17.10 GB in all).
+GEMM_DRAM_BYTES_PER_LAUNCH = 2.850e9
+
+# Expert-parallel workload (N > 1; weak scaling, the per-GPU work is fixed): 128 experts split evenly over the ranks,
+# hidden 4096, ffn 1536, SwiGLU, 32768 tokens per GPU routed top-8 (softmax over N(0,1) logits, 8 distinct experts per
+# token) = 262144 routed rows per GPU, delayed scaling with an amax history of 16.
+EP = dict(E=128, H=4096, F=1536, tokens_per_gpu=32768, topk=8,
+          name=("expert-parallel GroupedMLP (E=128 split over the ranks, hidden 4096, ffn 1536, SwiGLU, "
+                "32768 tokens/GPU top-8, all-to-all dispatch/combine)"))
+EP["rows_per_expert"] = EP["tokens_per_gpu"] * EP["topk"] // EP["E"]   # per source rank; sizes the CPU baseline sample
 
 
 def parse():
@@ -54,6 +70,7 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="auto", choices=["auto", "mixtral", "ep"])
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-extras", action="store_true", help="N = 1: skip the pad / library_gemm / fine_grained legs")
     p.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                    help="expert-parallel leg: copy-engine pushes into peer memory pipelined with the GEMMs, or NCCL all-to-all")
     p.add_argument("--ep-bf16-dispatch", action="store_true", help="peer transport: dispatch rows as bf16 instead of FP8")
@@ -83,6 +100,16 @@ def mixtral_workload(seed=0):
     sizes = torch.bincount(picks.reshape(-1), minlength=E)
     return dict(name="mixtral-8x7b-shaped GroupedMLP (E=8, hidden 4096, ffn 14336, SwiGLU, 16384 tokens top-2)",
                 E=E, H=H, F=F, tokens=tokens, topk=topk, sizes=sizes, rows=int(sizes.sum()))
+
+
+def fine_grained_workload(seed=3):
+    """Fine-grained MoE: 64 experts, hidden 2048, ffn 1408, SwiGLU, 8192 tokens top-6 = 49152 routed rows with
+    Zipf(s = 1.2) expert popularity, so many groups are small, empty or not multiples of 16."""
+    E, H, F, rows = 64, 2048, 1408, 49152
+    g = torch.Generator().manual_seed(seed)
+    p = 1.0 / torch.arange(1, E + 1, dtype=torch.float64) ** 1.2
+    idx = torch.multinomial((p / p.sum()).float(), rows, replacement=True, generator=g)
+    return dict(E=E, H=H, F=F, rows=rows, sizes=torch.bincount(idx, minlength=E))
 
 
 def mlp_flops(rows, H, F):
@@ -216,28 +243,31 @@ def timed_steps(fn, steps):
 
 
 class E2EPipeline:
-    """End-to-end loop through the public API with host buffers: every step copies its inputs (x, grad_out) from
-    pinned host memory and reads its results (out, grad_input) back to pinned host memory, all inside the timed
-    region.  Like an input pipeline with prefetch, the copies run on their own streams: step i+1's inputs are copied
-    while step i computes (two device input buffers), and step i's results are read while step i+1 computes."""
+    """End-to-end loop through the public API with host buffers: every step copies its inputs from pinned host memory
+    and reads its results back to pinned host memory, all inside the timed region.  Like an input pipeline with
+    prefetch, the copies run on their own streams: step i+1's inputs are copied while step i computes (two sets of
+    device input buffers), and step i's results are read while step i+1 computes.
 
-    def __init__(self, run_step, x_host, dy_host, out_host, gi_host, dev):
+    ``run_step(*device_inputs)`` returns the device tensors to read back, in the order of ``host_out``."""
+
+    def __init__(self, run_step, host_in, host_out, dev):
         self.run_step, self.dev = run_step, dev
-        self.hosts = (x_host, dy_host, out_host, gi_host)
+        self.host_in, self.host_out = list(host_in), list(host_out)
         self.h2d, self.d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        self.x = [torch.empty_like(x_host, device=dev).requires_grad_(True) for _ in range(2)]
-        self.dy = [torch.empty_like(dy_host, device=dev) for _ in range(2)]
+        self.bufs = [[torch.empty_like(h, device=dev) for h in self.host_in] for _ in range(2)]
         self.ready = [torch.cuda.Event() for _ in range(2)]
         self.done = [None, None]
-        self.keep = [None, None]   # results of the step that last used a buffer pair, alive until their read-back is done
+        self.keep = [None, None]   # results of the step that last used a buffer set, alive until their read-back is done
+        self.h2d_bytes = sum(h.numel() * h.element_size() for h in self.host_in)
+        self.d2h_bytes = sum(h.numel() * h.element_size() for h in self.host_out)
 
     def _prefetch(self, i):
         b = i % 2
         with torch.cuda.stream(self.h2d):
             if self.done[b] is not None:
-                self.h2d.wait_event(self.done[b])     # the step that last used this buffer has finished
-            self.x[b].data.copy_(self.hosts[0], non_blocking=True)
-            self.dy[b].copy_(self.hosts[1], non_blocking=True)
+                self.h2d.wait_event(self.done[b])     # the step that last used this buffer set has finished
+            for dst, src in zip(self.bufs[b], self.host_in):
+                dst.copy_(src, non_blocking=True)
             self.ready[b].record(self.h2d)
 
     def run(self, steps):
@@ -250,20 +280,19 @@ class E2EPipeline:
             cur.wait_event(self.ready[b])
             if self.keep[b] is not None:
                 # results may live in memory that is reused once they are dropped: drop them only after their copy
-                cur.wait_event(self.keep[b][2])
+                cur.wait_event(self.keep[b][1])
                 self.keep[b] = None
-            self.x[b].grad = None
-            out, gi = self.run_step(self.x[b], self.dy[b])
+            outs = self.run_step(*self.bufs[b])
             ev = torch.cuda.Event()
             ev.record(cur)
             self.done[b] = ev
             with torch.cuda.stream(self.d2h):
                 self.d2h.wait_event(ev)
-                self.hosts[2].copy_(out.detach(), non_blocking=True)
-                self.hosts[3].copy_(gi, non_blocking=True)
+                for dst, src in zip(self.host_out, outs):
+                    dst.copy_(src.detach(), non_blocking=True)
                 read = torch.cuda.Event()
                 read.record(self.d2h)
-            self.keep[b] = (out, gi, read)
+            self.keep[b] = (outs, read)
         cur.wait_stream(self.d2h)
         cur.wait_stream(self.h2d)
         self.done = [None, None]
@@ -302,15 +331,16 @@ def run_single(args):
         out.backward(dy_dev)
         return out
 
-    def step_on(x_in, dy_in):
+    def step_on(x_buf, dy_in):
         mlp.fc1_weight.grad = None
         mlp.fc2_weight.grad = None
+        x_in = x_buf.detach().requires_grad_(True)
         with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
             out = mlp(x_in, sizes)
         out.backward(dy_in)
         return out, x_in.grad
 
-    e2e = E2EPipeline(step_on, x_host, dy_host, out_host, gi_host, dev)
+    e2e = E2EPipeline(step_on, [x_host, dy_host], [out_host, gi_host], dev)
 
     sampler = ClockSampler(dev.index or 0)
     for _ in range(max(args.warmup, 3)):
@@ -349,8 +379,7 @@ def run_single(args):
         "frac_of_nominal_fp8_peak": value / NOMINAL_FP8_TFLOPS,
         "clocks": clocks.summary(),
         "e2e": {"value": flops * args.steps / secs_e2e / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": x_host.numel() * 2 + dy_host.numel() * 2,
-                "d2h_bytes_per_step": out_host.numel() * 2 + gi_host.numel() * 2,
+                "h2d_bytes_per_step": e2e.h2d_bytes, "d2h_bytes_per_step": e2e.d2h_bytes,
                 "ms_per_step": secs_e2e / args.steps * 1e3,
                 "how": "GroupedMlp forward + backward per step; inputs copied from pinned host memory and results read "
                        "back every step on side streams (next step's inputs prefetched during this step's compute)"},
@@ -370,7 +399,52 @@ def run_single(args):
         ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)
         line["cpu_baseline"] = {"value": ctf, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
                                 "sample": desc}
+    if not args.no_extras:
+        # free the step's tensors first: the microbenchmark holds about 20 GB
+        del mlp, x_dev, dy_dev, e2e, step, step_on
+        torch.cuda.empty_cache()
+        import bench_kernels
+
+        line["fine_grained"] = fine_grained_leg(fg, backend, dev, args.steps)
+        line["pad"] = bench_kernels.pad_suite(backend, dev)
+        line["pad"]["peak_hbm_gbs"] = {"measured_copy": peaks["hbm_gbs"], "nominal": 8000.0}
+        line["library_gemm"] = bench_kernels.library_gemm_suite(backend, dev, sizes.tolist())
+        backend.device_status()
     print(json.dumps(line), flush=True)
+
+
+def fine_grained_leg(fg, backend, dev, steps):
+    """The fine-grained MoE step (small, empty and ragged groups) through GroupedMlp: ms per step and TFLOP/s."""
+    wl = fine_grained_workload()
+    E, H, F, rows, sizes = wl["E"], wl["H"], wl["F"], wl["rows"], wl["sizes"]
+    torch.manual_seed(4)
+    mlp = fg.GroupedMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu")
+    with torch.no_grad():
+        mlp.fc1_weight.normal_(0.0, 0.02)
+        mlp.fc2_weight.normal_(0.0, 0.02)
+    x = torch.randn(rows, H, device=dev).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+    recipe = fg.DelayedScaling(amax_history_len=16)
+
+    def step():
+        mlp.fc1_weight.grad = mlp.fc2_weight.grad = x.grad = None
+        with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+            out = mlp(x, sizes)
+        out.backward(dy)
+
+    for _ in range(3):
+        step()
+    timings = []
+    backend.set_gemm_timings(timings)
+    secs = timed_steps(step, steps)
+    backend.set_gemm_timings(None)
+    gemm_ms = sum(s.elapsed_time(e) for s, e, _ in timings)
+    flops = mlp_flops(rows, H, F)
+    return {"workload": "fine-grained MoE (E=64, hidden 2048, ffn 1408, SwiGLU, 8192 tokens top-6, Zipf(1.2) loads)",
+            "group_sizes_min_median_max": [int(sizes.min()), int(sizes.median()), int(sizes.max())],
+            "empty_groups": int((sizes == 0).sum()), "ragged_groups": int((sizes % 16 != 0).sum()),
+            "ms_per_step": secs / steps * 1e3, "tflops": flops * steps / secs / 1e12,
+            "gemm_share_of_step": (gemm_ms / 1e3) / secs}
 
 
 def main():
@@ -384,18 +458,16 @@ def main():
             wl = mixtral_workload()
             reference_arm(args, wl["name"], wl["H"], wl["F"], wl["rows"] // wl["E"])
         else:
-            from fp8_gmm_b200 import ep_bench
-
-            reference_arm(args, ep_bench.WORKLOAD_NAME, ep_bench.H, ep_bench.F, ep_bench.ROWS_PER_EXPERT * 8)
+            reference_arm(args, EP["name"], EP["H"], EP["F"], EP["rows_per_expert"] * 8)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: fp8_gmm_b200 has no CPU path (use --impl reference for the CPU baseline)")
     if workload == "mixtral":
         run_single(args)
     else:
-        from fp8_gmm_b200 import ep_bench
+        import bench_ep
 
-        ep_bench.run(args, METRIC, measured_peaks(), ClockSampler, cpu_sample_step, run_cpu, E2EPipeline)
+        bench_ep.run(args, METRIC, EP, measured_peaks(), ClockSampler, cpu_sample_step, run_cpu)
 
 
 if __name__ == "__main__":

@@ -100,6 +100,7 @@ SYMBOLS = {
     "fp8gmm_set_gemm_variant": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "fp8gmm_device_status_async": (ctypes.c_int, [c_vp, c_vp]),
     "fp8gmm_set_wait_limits": (ctypes.c_int, [c_i64, c_i64]),
+    "fp8gmm_moe_topk": (ctypes.c_int, [c_vp, ctypes.c_int, c_i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, c_vp, c_vp, c_vp, c_vp]),
     "fp8gmm_moe_sort": (ctypes.c_int, [c_vp, c_i64, ctypes.c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "fp8gmm_moe_gather": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),
     "fp8gmm_moe_scatter": (ctypes.c_int, [c_vp, c_vp, c_vp, ctypes.c_int, c_i64, c_i64, c_vp, c_vp]),
@@ -111,6 +112,8 @@ SYMBOLS = {
     "fp8gmm_peer_copy_blocks": (ctypes.c_int, [ctypes.POINTER(CopyBlock), ctypes.c_int, c_vp]),
     "fp8gmm_peer_signal": (ctypes.c_int, [ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_uint32, c_vp]),
     "fp8gmm_peer_wait": (ctypes.c_int, [c_vp, ctypes.c_int, ctypes.c_uint32, c_vp]),
+    "fp8gmm_peer_reduce_scatter_bf16": (ctypes.c_int, [ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_int, c_i64, c_i64, ctypes.c_int, c_vp]),
+    "fp8gmm_peer_all_gather_bf16": (ctypes.c_int, [ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_int, c_i64, c_i64, c_vp, ctypes.c_int, c_vp]),
     "fp8gmm_delayed_scaling_update": (
         ctypes.c_int,
         [c_fp, c_fp, c_fp, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_int, c_vp],

@@ -66,10 +66,143 @@ __global__ void peer_wait_kernel(const uint32_t* flags, int count, uint32_t valu
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Sum of a bf16 buffer over the ranks of a tensor-parallel group, over peer memory (plain peer loads; no
+// multimem, no TMA).  The reference all-reduces the input gradient of its MLP with NCCL after the fc1 data-gradient
+// GEMM (fp8_gmm/grouped_mlp.py:300-303,323-324); here the GEMM writes its partial rows into a peer-mapped staging
+// buffer chunk by chunk and two light kernels per chunk finish the sum while the next chunk's GEMM runs:
+//   reduce-scatter  rank r sums slice r of the chunk over all ranks' staging buffers (fp32, ranks in ascending
+//                   order, one rounding to bf16) and stores it in its own staging buffer;
+//   all-gather      every rank reads slice s from rank s's staging buffer into its result tensor (local memory).
+// Every element is summed exactly once, by one rank, so all ranks end with identical bits.
+// ---------------------------------------------------------------------------------------------
+struct ReduceParams {
+  const uint4* bufs[kMaxPeers];  // staging buffer of every rank as mapped here
+  uint4* out;                    // reduce-scatter: this rank's staging buffer; all-gather: the result tensor
+  long long begin;               // first 16-byte vector of the chunk
+  long long vectors;             // 16-byte vectors in the chunk
+  long long per_rank;            // vectors per slice (the last slice may be shorter)
+  int world;
+  int rank;
+};
+
+__device__ __forceinline__ void accumulate8(float (&acc)[8], uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    acc[2 * j] += bf16_lo(w[j]);
+    acc[2 * j + 1] += bf16_hi(w[j]);
+  }
+}
+
+constexpr int kReduceBatch = 4;   // independent 16-byte loads a thread keeps in flight per rank (peer latency is microseconds)
+
+__global__ void __launch_bounds__(256) peer_reduce_scatter_kernel(const ReduceParams p) {
+  const long long lo = p.begin + p.rank * p.per_rank;
+  const long long end = p.begin + p.vectors;
+  const long long hi = lo + p.per_rank < end ? lo + p.per_rank : end;
+  const long long stride = 256ll * gridDim.x;
+  for (long long i0 = lo + blockIdx.x * 256ll + threadIdx.x; i0 < hi; i0 += stride * kReduceBatch) {
+    float acc[kReduceBatch][8];
+#pragma unroll
+    for (int u = 0; u < kReduceBatch; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    for (int r = 0; r < p.world; ++r) {
+      uint4 v[kReduceBatch];
+#pragma unroll
+      for (int u = 0; u < kReduceBatch; ++u) {
+        const long long i = i0 + u * stride;
+        v[u] = i < hi ? __ldcv(p.bufs[r] + i) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kReduceBatch; ++u) accumulate8(acc[u], v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kReduceBatch; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < hi)
+        p.out[i] = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                              pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) peer_all_gather_kernel(const ReduceParams p) {
+  const long long stride = 256ll * gridDim.x;
+  for (long long v0 = blockIdx.x * 256ll + threadIdx.x; v0 < p.vectors; v0 += stride * kReduceBatch) {
+    uint4 v[kReduceBatch];
+#pragma unroll
+    for (int u = 0; u < kReduceBatch; ++u) {
+      const long long i = v0 + u * stride;
+      if (i < p.vectors) v[u] = __ldcv(p.bufs[static_cast<int>(i / p.per_rank)] + p.begin + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kReduceBatch; ++u) {
+      const long long i = v0 + u * stride;
+      if (i < p.vectors) p.out[p.begin + i] = v[u];
+    }
+  }
+}
+
+int fill_reduce_params(ReduceParams* p, void* const* bufs, int world, int rank, int64_t elem_offset, int64_t numel, void* out,
+                       const char* name) {
+  FP8GMM_CHECK_ARG(bufs != nullptr && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "%s: bad group", name);
+  FP8GMM_CHECK_ARG(elem_offset >= 0 && numel >= 0 && elem_offset % 8 == 0 && numel % 8 == 0,
+                   "%s: offset and length must be multiples of 8 elements", name);
+  memset(p, 0, sizeof(*p));
+  for (int r = 0; r < world; ++r) {
+    FP8GMM_CHECK_ARG(bufs[r] != nullptr && reinterpret_cast<uintptr_t>(bufs[r]) % 16 == 0, "%s: buffer %d is NULL or unaligned", name, r);
+    p->bufs[r] = static_cast<const uint4*>(bufs[r]);
+  }
+  FP8GMM_CHECK_ARG(out != nullptr && reinterpret_cast<uintptr_t>(out) % 16 == 0, "%s: output is NULL or unaligned", name);
+  p->out = static_cast<uint4*>(out);
+  p->begin = elem_offset / 8;
+  p->vectors = numel / 8;
+  p->per_rank = (p->vectors + world - 1) / world;
+  if (p->per_rank == 0) p->per_rank = 1;
+  p->world = world;
+  p->rank = rank;
+  return FP8GMM_OK;
+}
+
+int reduce_grid(long long vectors, int max_ctas) {
+  const long long want = (vectors + 255) / 256;
+  const long long cap = max_ctas > 0 ? max_ctas : 64;
+  return static_cast<int>(want < 1 ? 1 : want < cap ? want : cap);
+}
+
 }  // namespace
 }  // namespace fp8gmm
 
 extern "C" {
+
+int fp8gmm_peer_reduce_scatter_bf16(void* const* bufs, int world, int rank, int64_t elem_offset, int64_t numel, int max_ctas,
+                                    void* stream) {
+  using namespace fp8gmm;
+  ReduceParams p;
+  const int rc = fill_reduce_params(&p, bufs, world, rank, elem_offset, numel, bufs ? bufs[rank < world && rank >= 0 ? rank : 0] : nullptr,
+                                    "peer_reduce_scatter_bf16");
+  if (rc != FP8GMM_OK) return rc;
+  if (numel == 0) return FP8GMM_OK;
+  peer_reduce_scatter_kernel<<<reduce_grid(p.per_rank, max_ctas), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  FP8GMM_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return FP8GMM_OK;
+}
+
+int fp8gmm_peer_all_gather_bf16(void* const* bufs, int world, int rank, int64_t elem_offset, int64_t numel, void* out, int max_ctas,
+                                void* stream) {
+  using namespace fp8gmm;
+  ReduceParams p;
+  const int rc = fill_reduce_params(&p, bufs, world, rank, elem_offset, numel, out, "peer_all_gather_bf16");
+  if (rc != FP8GMM_OK) return rc;
+  if (numel == 0) return FP8GMM_OK;
+  peer_all_gather_kernel<<<reduce_grid(p.vectors, max_ctas), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  FP8GMM_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return FP8GMM_OK;
+}
 
 int fp8gmm_peer_alloc(size_t bytes, void** ptr, void* handle) {
   using namespace fp8gmm;

@@ -12,12 +12,14 @@ import math
 
 import torch
 
-from . import backend
+from . import backend, tp
 from .grouped_linear import cast_weight_cached
 from .recipe import Fp8GmmBaseModule, get_fp8_te_dtype
 from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_sizes, to_torch_dtype
 
 _T, _M = Fp8TensorType, MetaTensorType
+# chunks of experts the fc1 data-gradient GEMM is cut into when its result is summed over a tensor-parallel group
+TP_CHUNKS = 4
 
 
 class _GroupedMlp(torch.autograd.Function):
@@ -140,8 +142,25 @@ class _GroupedMlp(torch.autograd.Function):
             metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScale), metas.get_meta_strided(_T.kGradOutputGroup2, _M.kAmax),
             in2=pre_act, activation=ctx.activation)
         dpre_scale_inv = metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScaleInv)
-        grad_input, handle = None, None
-        if ctx.input_requires_grad:
+        grad_input, handle, reducer = None, None, None
+        if ctx.input_requires_grad and ctx.has_tp and perm is None and tp.use_peer_reduction(ctx.tp_group):
+            # Tensor-parallel sum over peer memory, chunk by chunk behind the GEMM that produces the partial rows:
+            # each chunk of experts is written into the peer-mapped staging buffer and summed on a side stream while
+            # the next chunk and the fc1 weight gradient keep the tensor cores busy (fp8_gmm_b200/tp.py).
+            reducer = tp.TpReducer.setup(dev, ctx.tp_group)
+            rows = cumsums[-1]
+            partial = reducer.begin(rows, hidden)
+            grad_input = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+            for j0, j1 in tp.chunk_groups(cumsums, TP_CHUNKS):
+                r0, r1 = cumsums[j0], cumsums[j1]
+                if r1 > r0:
+                    backend.fp8_gmm(
+                        grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], group_sizes[j0:j1],
+                        metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScaleInv, j0),
+                        metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=partial[r0:r1], backward=True,
+                        b_is_kn=ctx.kn)
+                    reducer.reduce_rows(grad_input, r0, r1)
+        elif ctx.input_requires_grad:
             grad_input = backend.fp8_gmm(
                 grad_pre_fp8, fc1_w_t, group_sizes, dpre_scale_inv,
                 metas.get_meta_strided(_T.kForwardWeightGroup1, _M.kScaleInv), backward=True,
@@ -160,6 +179,8 @@ class _GroupedMlp(torch.autograd.Function):
                 grad_pre_fp8, input_t_fp8, cumsums, dpre_scale_inv, metas.get_meta_strided(_T.kForwardInputGroup1, _M.kScaleInv))
         if handle is not None:
             handle.wait()
+        if reducer is not None:
+            reducer.finish()
         return grad_input, grad_fc1_weight, grad_fc2_weight, None, None, None, None, None, None, None, None, None
 
 

@@ -156,12 +156,17 @@ class Fp8GmmBaseModule(torch.nn.Module):
                 amax_and_scale_update(meta, False)
         meta["update_amax_and_scale_bwd"] = True
 
-    # ---- checkpointing: FP8 state travels with state_dict so a resumed run reproduces the same bytes
+    # ---- checkpointing: FP8 state travels with state_dict so a resumed run reproduces the same bytes.
+    # The extra state holds tensors, numbers and strings only, so a checkpoint written with
+    # ``torch.save(model.state_dict())`` loads with ``torch.load``'s default ``weights_only=True``.
     def get_extra_state(self):
         if not self.fp8_meta_tensors_initialized:
             return None
         m = self.fp8_meta
-        state = {"num_gemms": m["num_gemms"], "recipe": m["recipe"]}
+        r = m["recipe"]
+        state = {"num_gemms": m["num_gemms"],
+                 "recipe": {"margin": r.margin, "interval": r.interval, "fp8_format": r.fp8_format.value,
+                            "amax_history_len": r.amax_history_len, "amax_compute_algo": r.amax_compute_algo}}
         for key in ("scaling_fwd", "scaling_bwd"):
             state[key] = {"scale": m[key].scale.cpu(), "scale_inv": m[key].scale_inv.cpu(),
                           "amax_history": m[key].amax_history.cpu()}
@@ -170,17 +175,33 @@ class Fp8GmmBaseModule(torch.nn.Module):
         return state
 
     def set_extra_state(self, state):
+        """Accepts what ``get_extra_state`` returns, and the key layout of Transformer Engine's modules
+        (``scale_fwd`` / ``scale_inv_fwd`` / ``amax_history_fwd`` and the ``_bwd`` counterparts) when it arrives as a
+        plain dictionary of tensors, so that FP8 state saved by the reference's modules can seed these."""
         if state is None:
             return
         device = next(self.parameters()).device
         m = self.fp8_meta
-        m["recipe"], m["num_gemms"] = state["recipe"], state["num_gemms"]
+        if "scale_fwd" in state and "scaling_fwd" not in state:
+            state = {"scaling_fwd": {"scale": state["scale_fwd"], "scale_inv": state["scale_inv_fwd"],
+                                     "amax_history": state["amax_history_fwd"]},
+                     "scaling_bwd": {"scale": state["scale_bwd"], "scale_inv": state["scale_inv_bwd"],
+                                     "amax_history": state["amax_history_bwd"]},
+                     "num_gemms": state["scale_fwd"].numel() // 3, "recipe": state.get("recipe")}
+        recipe = state.get("recipe")
+        if isinstance(recipe, dict):
+            recipe = DelayedScaling(margin=recipe["margin"], interval=recipe["interval"], fp8_format=Format(recipe["fp8_format"]),
+                                    amax_history_len=recipe["amax_history_len"], amax_compute_algo=recipe["amax_compute_algo"])
+        elif recipe is None:
+            recipe = DelayedScaling(amax_history_len=state["scaling_fwd"]["amax_history"].shape[0])
+        m["recipe"], m["num_gemms"] = recipe, int(state["num_gemms"])
         for key, per in (("scaling_fwd", 3), ("scaling_bwd", 2)):
             meta = Fp8Meta(per * m["num_gemms"], state[key]["amax_history"].shape[0], device)
             meta.scale.copy_(state[key]["scale"])
             meta.scale_inv.copy_(state[key]["scale_inv"])
             meta.amax_history.copy_(state[key]["amax_history"])
             m[key] = meta
-        for key in ("update_amax_and_scale_fwd", "update_amax_and_scale_bwd", "step_fwd", "step_bwd"):
-            m[key] = state[key]
+        defaults = {"update_amax_and_scale_fwd": True, "update_amax_and_scale_bwd": True, "step_fwd": 0, "step_bwd": 0}
+        for key, default in defaults.items():
+            m[key] = state.get(key, default)
         self.fp8_meta_tensors_initialized = True

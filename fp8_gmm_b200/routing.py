@@ -4,11 +4,13 @@ The reference's example takes these from megablocks (``mega_ops.sort / histogram
 scatter``, reference fp8_gmm/example.py:26-32,52,59); megablocks is not a dependency of this package, so the same
 calls are provided here on this package's kernels (fp8_gmm_b200/csrc/routing.cu), with the same argument order:
 
+    multiplier, selected_experts = topk(scores, top_k, moe_renorm)
     indices, bin_ids, bins, tokens_per_expert = indices_and_bins(top_experts, n_experts)
     rows = gather(x, indices, bin_ids, bins, top_k)             # rows sorted by expert: what GroupedMlp consumes
     out = scatter(expert_out, indices, bin_ids, weights, bins, top_k)
 
-``gather`` and ``scatter`` are differentiable (w.r.t. the rows and, for scatter, the router weights).
+``gather`` and ``scatter`` are differentiable (w.r.t. the rows and, for scatter, the router weights), ``topk`` w.r.t.
+the logits.
 """
 import torch
 
@@ -25,6 +27,46 @@ class Routing:
     def __init__(self, indices, bin_ids, bins, tokens_per_expert, inverse):
         self.indices, self.bin_ids, self.bins = indices, bin_ids, bins
         self.tokens_per_expert, self.inverse = tokens_per_expert, inverse
+
+
+class _TopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, scores, top_k, renorm):
+        scores = scores.contiguous()
+        tokens, n_experts = scores.shape
+        dev = scores.device
+        probs = torch.empty(tokens, n_experts, dtype=torch.float32, device=dev)
+        weights = torch.empty(tokens, top_k, dtype=torch.float32, device=dev)
+        experts = torch.empty(tokens, top_k, dtype=torch.int32, device=dev)
+        check(lib.fp8gmm_moe_topk(scores.data_ptr(), int(scores.dtype == torch.bfloat16), tokens, n_experts, top_k, int(renorm),
+                                  probs.data_ptr(), weights.data_ptr(), experts.data_ptr(), _stream()), "moe_topk")
+        picked = experts.long()
+        ctx.save_for_backward(probs, picked, weights)
+        ctx.renorm, ctx.in_dtype = renorm, scores.dtype
+        ctx.mark_non_differentiable(picked)
+        return weights, picked
+
+    @staticmethod
+    def backward(ctx, grad_w, _):
+        # (tokens x experts) is tiny next to the rows: plain torch ops
+        probs, picked, weights = ctx.saved_tensors
+        grad_w = grad_w.float()
+        if ctx.renorm:   # weights = p_sel / sum(p_sel)
+            p_sel = probs.gather(1, picked)
+            total = p_sel.sum(1, keepdim=True)
+            grad_w = (grad_w - (grad_w * weights).sum(1, keepdim=True)) / total
+        grad_p = torch.zeros_like(probs).scatter_(1, picked, grad_w)
+        grad_logits = probs * (grad_p - (grad_p * probs).sum(1, keepdim=True))
+        return grad_logits.to(ctx.in_dtype), None, None
+
+
+def topk(scores, top_k, moe_renorm=False):
+    """Router of the reference's example (fp8_gmm/example.py:14-23) as one kernel: softmax over the experts in fp32,
+    the ``top_k`` largest probabilities (descending) and their expert ids, renormalised to sum to one when
+    ``moe_renorm``.  ``scores``: (tokens, n_experts) CUDA float32 or bfloat16.  Returns (multiplier fp32
+    (tokens, top_k), selected_experts int64 (tokens, top_k)); any top_k up to n_experts (the reference asserts 1 or 2)."""
+    assert scores.is_cuda and scores.dim() == 2 and scores.dtype in (torch.float32, torch.bfloat16)
+    return _TopK.apply(scores, int(top_k), bool(moe_renorm))
 
 
 def sort_by_expert(top_expert, n_experts):

@@ -350,10 +350,20 @@ int fp8gmm_delayed_scaling_update(float* amax_history, float* scale, float* scal
  * :52,:87,:118 gather, :59,:92,:121 scatter).  All pointers are device memory; rows are bf16.
  * ---------------------------------------------------------------------------------------------- */
 
+/* Router (reference fp8_gmm/example.py:14-23: softmax in fp32 over the expert logits, torch.topk, optional
+ * renormalisation): logits (tokens x num_experts) fp32 or bf16 -> weights (tokens x top_k) fp32, the top_k largest
+ * probabilities in descending order (equal values: lower expert id first), divided by their sum when `renormalize`;
+ * experts (tokens x top_k) int32 their ids; probs (tokens x num_experts) fp32 the full softmax, or NULL.
+ * num_experts <= 1024. */
+int fp8gmm_moe_topk(const void* logits, int logits_are_bf16, int64_t tokens, int num_experts, int top_k, int renormalize,
+                    float* probs, float* weights, int32_t* experts, void* stream);
+
 /* Stable counting sort of n = tokens * top_k expert ids (int32, values in [0, num_experts)):
  *   indices[i]  flat (token, slot) position held by sorted row i        bin_ids[i]  expert of sorted row i
  *   inverse[p]  sorted row of flat position p                           tokens_per_expert[e], bins[e] = inclusive cumsum
- * Equal ids keep their order, so the result is deterministic. */
+ * Equal ids keep their order, so the result is deterministic.  An id outside [0, num_experts) is reported through the
+ * device status word (see fp8gmm_device_status); its row is left out of the permutation (indices / inverse hold -1
+ * there) and the gather / scatter / rowdot kernels skip such entries instead of dereferencing them. */
 int fp8gmm_moe_sort(const int32_t* expert_ids, int64_t n, int num_experts, int32_t* indices, int32_t* bin_ids,
                     int32_t* inverse, int64_t* bins, int64_t* tokens_per_expert, void* stream);
 
@@ -406,6 +416,24 @@ int fp8gmm_peer_signal(uint32_t* const* flags, int count, uint32_t value, void* 
  * reached `value` (compared modulo 2^32).  The wait is bounded (two seconds unless fp8gmm_set_wait_limits changed
  * it); when it runs out the kernel sets a bit in the device status word (see fp8gmm_device_status) and returns. */
 int fp8gmm_peer_wait(const uint32_t* flags, int count, uint32_t value, void* stream);
+
+/*
+ * Sum of a bf16 buffer over the ranks of a tensor-parallel group in two steps over peer memory (plain peer loads,
+ * issued by a few CTAs that run beside the GEMMs).  Replaces the NCCL all-reduce of the MLP's input gradient
+ * (reference fp8_gmm/grouped_mlp.py:300-303,323-324) so that it proceeds chunk by chunk behind the fc1 data-gradient
+ * GEMM.  `bufs` is a HOST array of `world` device addresses: the same staging buffer on every rank as mapped into
+ * this process (fp8gmm_peer_alloc / fp8gmm_peer_open), bufs[rank] being the local one.  The element range
+ * [elem_offset, elem_offset + numel) (multiples of 8) is cut into `world` equal slices of 16-byte vectors.
+ *   reduce_scatter: slice `rank` of bufs[rank] = sum over r (ascending, fp32, one rounding) of slice `rank` of bufs[r];
+ *   all_gather:     out[range] (local memory laid out like the staging buffer) = slice s taken from bufs[s], all s.
+ * The caller orders the steps across ranks (fp8gmm_peer_signal / fp8gmm_peer_wait): every rank's partial sums must
+ * be complete before any reduce_scatter of the range starts, every reduce_scatter before any all_gather.
+ * max_ctas: upper bound on the CTAs used (0 = 64).
+ */
+int fp8gmm_peer_reduce_scatter_bf16(void* const* bufs, int world, int rank, int64_t elem_offset, int64_t numel, int max_ctas,
+                                    void* stream);
+int fp8gmm_peer_all_gather_bf16(void* const* bufs, int world, int rank, int64_t elem_offset, int64_t numel, void* out, int max_ctas,
+                                void* stream);
 
 #ifdef __cplusplus
 }

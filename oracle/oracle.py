@@ -323,6 +323,16 @@ def current_scale(x, dtype):
 # Router-side permutation (reference fp8_gmm/example.py:26-32,52,59: megablocks sort / histogram /
 # inclusive_cumsum / gather / scatter, restated from their call sites; megablocks itself is absent: parity unpinned)
 # ------------------------------------------------------------------------------------------------
+def moe_topk(scores, top_k, moe_renorm=False):
+    """Router of the reference's example, verbatim in meaning (fp8_gmm/example.py:14-23): fp32 softmax, torch.topk,
+    optional renormalisation.  Returns (multiplier, selected_experts)."""
+    weights = torch.nn.functional.softmax(scores, dim=1, dtype=torch.float)
+    multiplier, selected = torch.topk(weights, top_k)
+    if moe_renorm:
+        multiplier = multiplier / multiplier.sum(dim=-1, keepdim=True)
+    return multiplier, selected
+
+
 def moe_sort(top_expert, n_experts):
     """Stable sort of the flat expert ids: (indices, bin_ids, bins, tokens_per_expert, inverse)."""
     ids = top_expert.reshape(-1).to(torch.int64)

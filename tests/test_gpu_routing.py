@@ -98,3 +98,79 @@ def test_moe_block_like_the_reference_example(cuda):
     assert torch.isfinite(x.grad.float()).all() and x.grad.abs().sum() > 0
     assert gate.weight.grad is not None and torch.isfinite(gate.weight.grad.float()).all()
     assert mlp.fc1_weight.grad is not None
+
+
+@pytest.mark.parametrize("tokens,E,top_k,renorm,dtype", [
+    (2048, 8, 2, False, torch.float32),      # the reference example's router: top-2 of 8
+    (2048, 8, 2, True, torch.float32),
+    (333, 16, 1, False, torch.bfloat16),
+    (1024, 128, 8, True, torch.float32),     # the expert-parallel workload's router
+    (100, 64, 6, False, torch.bfloat16),
+    (17, 1000, 40, True, torch.float32),     # more picks than a warp has lanes
+])
+def test_topk_router_matches_oracle(cuda, tokens, E, top_k, renorm, dtype):
+    """softmax (fp32) + top-k + optional renormalisation as in the reference example (fp8_gmm/example.py:14-23).
+    Weights within 2e-6 relative (the warp's summation order differs from torch's); expert ids exact wherever no two
+    of the probabilities involved are within rounding of each other (equal logits may be named in either order)."""
+    from fp8_gmm_b200 import routing
+
+    g = torch.Generator().manual_seed(tokens + E)
+    scores = (torch.randn(tokens, E, generator=g) * 2.0).to(dtype)
+    want_w, want_e = O.moe_topk(scores, top_k, renorm)
+    got_w, got_e = routing.topk(scores.to(cuda), top_k, renorm)
+    assert got_w.dtype == torch.float32 and got_e.dtype == torch.int64
+    probs = torch.softmax(scores.float(), 1)
+    # the weights are the k largest probabilities whichever of several equal experts is named (bf16 logits tie often)
+    assert torch.allclose(got_w.cpu(), want_w, rtol=2e-6, atol=1e-9)
+    picked = probs.gather(1, got_e.cpu())
+    if renorm:
+        picked = picked / picked.sum(1, keepdim=True)
+    assert torch.allclose(picked, got_w.cpu(), rtol=2e-6, atol=1e-9)          # ids and weights belong together
+    assert all(len(set(row)) == top_k for row in got_e.cpu().tolist())        # distinct experts per token
+    srt = probs.sort(1, descending=True).values
+    gaps = (srt[:, :-1] - srt[:, 1:])[:, :top_k].min(1).values          # smallest gap among the picks and the runner-up
+    clear = gaps > 1e-6 * srt[:, 0]
+    assert torch.equal(got_e.cpu()[clear], want_e[clear])               # no ties: the ids are determined
+    if renorm:
+        assert torch.allclose(got_w.sum(1).cpu(), torch.ones(tokens), atol=1e-6)
+
+
+def test_topk_router_gradient(cuda):
+    from fp8_gmm_b200 import routing
+
+    g = torch.Generator().manual_seed(9)
+    scores = torch.randn(64, 8, generator=g)
+    up = torch.randn(64, 2, generator=g)
+    for renorm in (False, True):
+        s_ref = scores.clone().requires_grad_(True)
+        w_ref, _ = O.moe_topk(s_ref, 2, renorm)
+        (w_ref * up).sum().backward()
+        s = scores.to(cuda).requires_grad_(True)
+        w, _ = routing.topk(s, 2, renorm)
+        (w * up.to(cuda)).sum().backward()
+        assert torch.allclose(s.grad.cpu(), s_ref.grad, rtol=1e-4, atol=1e-6)
+
+
+def test_invalid_expert_id_is_reported_not_dereferenced(cuda):
+    """One id outside [0, num_experts): the sort reports it through the status word, leaves the row out of the
+    permutation, and gather / scatter skip the unset entries instead of using them as row numbers."""
+    from fp8_gmm_b200 import _lib, backend, routing
+
+    E, top_k, tokens, H = 4, 2, 50, 64
+    ids = _ids(tokens, top_k, E, 5)
+    ids[11] = 9
+    backend.device_status()
+    r = routing.sort_by_expert(ids.to(cuda), E)
+    assert _lib.lib.fp8gmm_device_status(torch.cuda.current_stream().cuda_stream) == 4
+    assert int(r.bins[-1]) == tokens * top_k - 1
+    assert int(r.inverse[11]) == -1 and int(r.indices[-1]) == -1
+    x = randn_bf16((tokens, H), 6).to(cuda)
+    rows = routing.gather(x, r.indices, r.bin_ids, r.bins, top_k)
+    back = routing.scatter(rows, r.indices, r.bin_ids, None, r.bins, top_k)
+    torch.cuda.synchronize()
+    assert _lib.lib.fp8gmm_device_status(torch.cuda.current_stream().cuda_stream) == 4
+    keep = torch.ones(tokens, dtype=torch.bool)
+    keep[11 // top_k] = False
+    want = (x.float() * top_k).to(torch.bfloat16)
+    assert torch.equal(back[keep.to(cuda)], want[keep.to(cuda)])      # every other token is untouched by the bad id
+    backend.device_status()

@@ -72,3 +72,63 @@ def test_router_oracle_round_trip():
     assert torch.equal(rows[inverse].reshape(tokens, top_k, H)[:, 0], x)
     out = O.moe_scatter(rows, inverse, top_k)
     assert torch.allclose(out.float(), 3 * x.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_tensor_parallel_chunks_cover_all_groups_in_order():
+    """Chunk bookkeeping of the tensor-parallel reduction: contiguous runs of groups, every group in exactly one
+    chunk, about equal row counts, empty groups and fewer groups than chunks handled."""
+    from fp8_gmm_b200.tp import chunk_groups
+
+    for sizes, chunks in [([4122, 4066, 4022, 4015, 4148, 4194, 4168, 4033], 4), ([5, 0, 0, 900, 1], 4), ([7], 4), ([0, 0, 0], 2),
+                          ([10] * 64, 4), ([], 4), ([1000, 1, 1, 1, 1, 1, 1, 1000], 3)]:
+        cums = [0]
+        for s in sizes:
+            cums.append(cums[-1] + s)
+        out = chunk_groups(cums, chunks)
+        assert len(out) <= max(chunks, 1)
+        flat = [g for a, b in out for g in range(a, b)]
+        assert flat == list(range(len(sizes)))
+        assert all(b > a for a, b in out)
+    even = chunk_groups([0, 100, 200, 300, 400, 500, 600, 700, 800], 4)
+    assert even == [(0, 2), (2, 4), (4, 6), (6, 8)]
+
+
+def test_fp8_state_survives_torch_save_and_default_torch_load(tmp_path):
+    """The FP8 recipe state is part of state_dict and holds tensors / numbers / strings only, so a checkpoint written
+    with torch.save loads with torch.load's default arguments (weights_only=True) and restores scales, amax history,
+    step counters and the recipe; a Transformer-Engine-style dictionary of meta tensors is accepted as well."""
+    import torch
+
+    import fp8_gmm_b200 as fg
+    from fp8_gmm_b200.recipe import Format
+
+    recipe = fg.DelayedScaling(margin=1, interval=2, fp8_format=Format.HYBRID, amax_history_len=5, amax_compute_algo="most_recent")
+    a = fg.GroupedMlp(32, 64, 3, torch.bfloat16, device="cpu", activation="swiglu")
+    with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+        a._init_fp8_meta(6, torch.device("cpu"))
+    g = torch.Generator().manual_seed(0)
+    for key in ("scaling_fwd", "scaling_bwd"):
+        meta = a.fp8_meta[key]
+        meta.scale.copy_(torch.rand(meta.scale.shape, generator=g) + 0.5)
+        meta.scale_inv.copy_(1.0 / meta.scale)
+        meta.amax_history.copy_(torch.rand(meta.amax_history.shape, generator=g))
+    a.fp8_meta["step_fwd"], a.fp8_meta["step_bwd"] = 7, 6
+    a.fp8_meta["update_amax_and_scale_fwd"] = True
+    path = tmp_path / "ckpt.pt"
+    torch.save(a.state_dict(), path)
+    loaded = torch.load(path)                       # default arguments: weights_only=True
+    b = fg.GroupedMlp(32, 64, 3, torch.bfloat16, device="cpu", activation="swiglu")
+    b.load_state_dict(loaded)
+    assert torch.equal(a.fc1_weight, b.fc1_weight)
+    for key in ("scaling_fwd", "scaling_bwd"):
+        for field in ("scale", "scale_inv", "amax_history"):
+            assert torch.equal(getattr(a.fp8_meta[key], field), getattr(b.fp8_meta[key], field))
+    assert b.fp8_meta["recipe"] == recipe and b.fp8_meta["step_fwd"] == 7 and b.fp8_meta["step_bwd"] == 6
+    assert b.fp8_meta["update_amax_and_scale_fwd"] is True
+    # Transformer Engine's key layout
+    te_style = {f"{name}_{d}": getattr(a.fp8_meta[f"scaling_{d}"], name).clone() for d in ("fwd", "bwd")
+                for name in ("scale", "scale_inv", "amax_history")}
+    c = fg.GroupedMlp(32, 64, 3, torch.bfloat16, device="cpu", activation="swiglu")
+    c.set_extra_state(te_style)
+    assert c.fp8_meta["num_gemms"] == 6 and torch.equal(c.fp8_meta["scaling_bwd"].scale, a.fp8_meta["scaling_bwd"].scale)
+    assert c.fp8_meta["recipe"].amax_history_len == 5
