@@ -21,7 +21,9 @@
 //     decodes (group, m-tile, n-tile) from prefix sums held in the kernel parameter block.  Tiles are
 //     ordered group-major and, inside a group, in super-rows of 4096 rows (2048 for long contractions) with
 //     m fastest, so the concurrently running tiles share operand tiles through L2;
-//   * no cluster launch and no multicast: every CTA loads its own operands.
+//   * no multicast: every CTA loads its own operands.  (Asking the TMA unit to prefetch the K block 8-16 steps ahead
+//     into L2 was measured 10 % slower, whether every CTA prefetched its boxes or one CTA per distinct box did: the
+//     extra requests cost the TMA queue more than the shorter fill latency gives back.)
 // Two addressing modes share the kernel: "rows" (forward/dgrad: groups are row blocks of one A matrix,
 // B is (G,N,K)) and "wgrad" (each group has its own pair of TMA descriptors in global memory because the
 // padded-transposed operand blocks have a group-dependent row pitch; contraction length varies per group).
@@ -586,9 +588,18 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       // A warp whose 32 rows all belong to the tile stages its results in shared memory and lets TMA write
       // them (full 128-byte lines per row instead of 32 scattered 16-byte stores per instruction).
       const int tile_cols = p.activation == FP8GMM_ACT_SWIGLU ? kBlockN / 2 : kBlockN;
-      const bool use_tma = p.tma_store != 0 && t.valid_rows - quad * 32 >= 32 && t.valid_cols == tile_cols;
+      bool use_tma = p.tma_store != 0 && t.valid_rows - quad * 32 >= 32 && t.valid_cols == tile_cols;
       const uint32_t stage0 = staging_addr + static_cast<uint32_t>(quad) * 8192u;
-      const int row_coord = static_cast<int>((p.mode == kModeWgrad ? static_cast<int64_t>(t.group) * p.m_fixed : 0) + t.row0) + quad * 32;
+      int row_coord = static_cast<int>((p.mode == kModeWgrad ? static_cast<int64_t>(t.group) * p.m_fixed : 0) + t.row0) + quad * 32;
+      if (use_tma && p.row_map != nullptr) {
+        // A row map moves whole runs of rows (blocks of one expert and one source rank): a slab whose 32 rows stay
+        // consecutive at their destination still leaves as TMA boxes, at the mapped row; only slabs that straddle
+        // the end of a run take the per-thread stores below.
+        const int mine = p.row_map[out_row];
+        const int first = __shfl_sync(0xFFFFFFFFu, mine, 0);
+        use_tma = __all_sync(0xFFFFFFFFu, mine == first + lane);
+        row_coord = first;
+      }
       if (p.activation == FP8GMM_ACT_NONE && use_tma) {
         const int col_base = t.nt * kBlockN;
 #pragma unroll 1
@@ -889,11 +900,14 @@ int encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 
 // Process-wide switches of the GEMM launches.  Defaults come from the environment, read once when the library is
 // first used (FP8GMM_GEMM_CTAS=1|2 forces the tile shape, FP8GMM_GEMM_EPILOGUE=direct turns the TMA-store epilogue
-// off, FP8GMM_GEMM_NO_TAIL_SPLIT keeps short group tails on pair tiles); fp8gmm_set_gemm_variant changes them later.
+// off, FP8GMM_GEMM_NO_TAIL_SPLIT keeps short group tails on pair tiles, FP8GMM_GEMM_SUPER_ROWS=short,long sets the
+// super-row heights of the tile order); fp8gmm_set_gemm_variant changes the first three later.
 struct Tuning {
   int ctas = 0;             // 0 = choose per call, 1 = single-CTA 128-row tiles, 2 = CTA-pair 256-row tiles
   bool tail_split = true;   // pair tiles: tails of at most 128 rows go to a second launch on 128-row tiles
   bool tma_epilogue = true; // full 32-row slabs leave through shared memory + TMA stores
+  int super_rows_short = kSuperRowsShortK;  // rows per super-row of the tile order, contraction <= kLongK
+  int super_rows_long = kSuperRowsLongK;    // ... and above (FP8GMM_GEMM_SUPER_ROWS=short,long; multiples of 256)
 };
 Tuning& tuning() {
   static Tuning t = [] {
@@ -903,6 +917,12 @@ Tuning& tuning() {
     e = getenv("FP8GMM_GEMM_EPILOGUE");
     v.tma_epilogue = !(e != nullptr && e[0] == 'd');
     v.tail_split = getenv("FP8GMM_GEMM_NO_TAIL_SPLIT") == nullptr;
+    e = getenv("FP8GMM_GEMM_SUPER_ROWS");
+    int a = 0, b = 0;
+    if (e != nullptr && sscanf(e, "%d,%d", &a, &b) == 2 && a >= 256 && b >= 256 && a % 256 == 0 && b % 256 == 0) {
+      v.super_rows_short = a;
+      v.super_rows_long = b;
+    }
     return v;
   }();
   return t;
@@ -1021,7 +1041,7 @@ int wgrad_launch(const fp8gmm_wgrad_args* a, cudaStream_t s, const char* name, W
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = p.tile_start[a->num_groups];
   p.idesc = make_idesc(a->a_format, a->b_format, ctas, form == kWgradRowMajor, form == kWgradRowMajor);
-  p.super_tiles = kSuperRowsShortK / (kBlockM * ctas);
+  p.super_tiles = tuning().super_rows_short / (kBlockM * ctas);
   if (tuning().tma_epilogue) {
     const int rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(a->num_groups) * a->n, static_cast<uint64_t>(a->k));
     if (rc != FP8GMM_OK) return rc;
@@ -1165,8 +1185,8 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.tiles_n = static_cast<int>(tiles_n);
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas, false, a->b_layout == 1);
-  p.super_tiles = (a->k > kLongK ? kSuperRowsLongK : kSuperRowsShortK) / tile_m;
-  if (a->c_row_map == nullptr && a->activation != FP8GMM_ACT_GELU && tuning().tma_epilogue) {
+  p.super_tiles = (a->k > kLongK ? tuning().super_rows_long : tuning().super_rows_short) / tile_m;
+  if (a->activation != FP8GMM_ACT_GELU && tuning().tma_epilogue) {
     rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
     if (rc != FP8GMM_OK) return rc;
     p.tma_store = 1;
@@ -1187,7 +1207,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
     p.tile_start[a->num_groups] = t;
     p.total_tiles = t;
     p.idesc = make_idesc(a->a_format, a->b_format, 1, false, a->b_layout == 1);
-    p.super_tiles = (a->k > kLongK ? kSuperRowsLongK : kSuperRowsShortK) / kBlockM;
+    p.super_tiles = (a->k > kLongK ? tuning().super_rows_long : tuning().super_rows_short) / kBlockM;
     rc = launch(p, 1, static_cast<cudaStream_t>(stream));
     if (rc != FP8GMM_OK) return rc;
   }

@@ -85,6 +85,8 @@ __global__ void __launch_bounds__(kThreads, 3) multi_pad_kernel(const __grid_con
   const int t = upper_slot(args.tile_start, args.num, tile);
   const PadDesc& d = args.d[t];
   const int local = tile - args.tile_start[t];
+  // column tiles fastest (a banded, rows-fastest order that lets consecutive CTAs write consecutive pieces of the same
+  // transposed columns was measured: no gain for the transposes, 2 % slower for the cast)
   const int tile_row = (local / d.tiles_n) * kTileRows;
   const int tile_col = (local % d.tiles_n) * kTileCols;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -260,8 +262,10 @@ __global__ void __launch_bounds__(kThreads, 3) multi_pad_kernel(const __grid_con
 // column the eight 16-byte chunks are XOR-swizzled with the writer's lane & 7 (as in the cast kernel) and the
 // four words of a chunk with lane >> 3, which makes the 32-bit stores of a warp hit 32 different banks.
 // ---------------------------------------------------------------------------------------------
-template <int kMode, int kFormat>
-__global__ void __launch_bounds__(kThreads, 2) act_pad_kernel(const __grid_constant__ PadArgs args) {
+// kWithT = false is the form without a transposed copy (what the modules launch by default, since the weight-gradient
+// GEMM reads the row-major FP8 rows): no shared-memory tile, no byte packing, three CTAs per SM.
+template <int kMode, int kFormat, bool kWithT>
+__global__ void __launch_bounds__(kThreads, kWithT ? 2 : 3) act_pad_kernel(const __grid_constant__ PadArgs args) {
   static_assert(kWarps == 8, "the word swizzle below assumes 8 warps (128-row tiles)");
   constexpr int kHalves = (kMode == kDswiglu) ? 2 : 1;
   constexpr int kHalfBytes = kTileCols * kTileRows;
@@ -362,14 +366,16 @@ __global__ void __launch_bounds__(kThreads, 2) act_pad_kernel(const __grid_const
               if (col0 + j < cols) p[j] = (uint8_t)(((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xFFu);
           }
         }
+        if (kWithT) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t byte = ((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xFFu;
-          tw[h][j] |= byte << (8 * r);
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t byte = ((j < 4 ? lo : hi) >> (8 * (j & 3))) & 0xFFu;
+            tw[h][j] |= byte << (8 * r);
+          }
         }
       }
     }
-    if (d.out_t != nullptr) {
+    if (kWithT && d.out_t != nullptr) {
 #pragma unroll
       for (int h = 0; h < kHalves; ++h)
 #pragma unroll
@@ -381,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 2) act_pad_kernel(const __grid_const
     }
   }
 
-  if (d.out_t != nullptr) {
+  if (kWithT && d.out_t != nullptr) {
     __syncthreads();
     const int padded_rows = d.padded_rows;
 #pragma unroll
@@ -429,10 +435,16 @@ __global__ void __launch_bounds__(kThreads, 2) act_pad_kernel(const __grid_const
 
 template <int kMode, int kFormat>
 int launch_act(const PadArgs& args, cudaStream_t s) {
-  constexpr int kSmem = kTileCols * kTileRows * (kMode == kDswiglu ? 2 : 1);
-  if (kSmem > 48 * 1024)
-    FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(act_pad_kernel<kMode, kFormat>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-  act_pad_kernel<kMode, kFormat><<<args.tile_start[args.num], kThreads, kSmem, s>>>(args);
+  bool any_t = false;
+  for (int i = 0; i < args.num; ++i) any_t |= args.d[i].out_t != nullptr;
+  if (!any_t) {
+    act_pad_kernel<kMode, kFormat, false><<<args.tile_start[args.num], kThreads, 0, s>>>(args);
+  } else {
+    constexpr int kSmem = kTileCols * kTileRows * (kMode == kDswiglu ? 2 : 1);
+    if (kSmem > 48 * 1024)
+      FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(act_pad_kernel<kMode, kFormat, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    act_pad_kernel<kMode, kFormat, true><<<args.tile_start[args.num], kThreads, kSmem, s>>>(args);
+  }
   FP8GMM_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return FP8GMM_OK;

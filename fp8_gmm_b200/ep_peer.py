@@ -127,6 +127,45 @@ class PeerPlan:
             self._lists[key] = _block_arrays(self.combine_blocks(chunk))
         return self._lists[key]
 
+    def staged_combine(self):
+        """Layout that lets one copy per (home rank, chunk) return the results.  At the owner rows are expert-major
+        (inside an expert ordered by source rank); a home rank wants the rows of a chunk's experts back to back (it
+        holds them sorted by global expert).  So the GEMM epilogue that produces a chunk's result rows writes them
+        *source-major inside the chunk* -- all rows of source 0 for the chunk's experts, then source 1, ... -- through
+        its row map, and the rows of one (home rank, chunk) form one contiguous run on both sides.
+
+        Returns (row_map, copies): ``row_map`` int32 numpy (rows_local,), expert-major row -> staged row, relative to
+        the first row of the row's chunk; ``copies[chunk]`` = four int64 arrays (home rank, dst_row at home, staged
+        src_row here, rows), peers in the staggered order."""
+        key = "stage"
+        if key not in self._lists:
+            El, r = self.experts_local, self.rank
+            by = self.by_owner[r].numpy()            # (El, P): rows of local expert j that came from source s
+            exp_off = self.exp_off[r].numpy()        # (El + 1,)
+            blk_off = self.blk_off[r].numpy()        # (El, P): expert-major start of block (j, s)
+            send_off = self.send_off.numpy()         # (P, E + 1)
+            row_map = np.empty(int(exp_off[-1]), dtype=np.int32)
+            copies = {}
+            order = np.asarray(self._peer_order(), dtype=np.int64)
+            for (j0, j1) in self.chunks:
+                r0, r1 = int(exp_off[j0]), int(exp_off[j1])
+                cnt = by[j0:j1]
+                per_src = cnt.sum(0)
+                src_base = np.cumsum(per_src) - per_src
+                staged = src_base[None, :] + (np.cumsum(cnt, 0) - cnt)      # staged start of block (j, s), chunk-relative
+                delta = (staged - (blk_off[j0:j1] - r0)).reshape(-1)
+                row_map[r0:r1] = np.arange(r1 - r0, dtype=np.int64) + np.repeat(delta, cnt.reshape(-1))
+                copies[(j0, j1)] = (order, send_off[order, r * El + j0], r0 + src_base[order], per_src[order])
+            self._lists[key] = (row_map, copies)
+        return self._lists[key]
+
+    def staged_row_map(self, device):
+        """The staged row map on the device (uploaded once per plan)."""
+        key = ("stage_dev", device.index)
+        if key not in self._lists:
+            self._lists[key] = torch.from_numpy(self.staged_combine()[0]).to(device)
+        return self._lists[key]
+
     def combine_blocks(self, chunk):
         """(home rank, dst_row at home, src_row here, rows) for the result rows this rank returns for one chunk."""
         key = ("c", chunk)
@@ -457,6 +496,9 @@ class _PeerEpMlp(torch.autograd.Function):
         out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
         out = ectx.result_tensor(plan.out_ids[plan.rank], plan.rows_own, hidden)
         out_np = np.asarray([ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+        # results are written source-major inside each chunk by the fc2 epilogue, so one copy per (home rank, chunk)
+        # takes them home (blocks of tens of MiB instead of one block per expert: the copy engines run faster on them)
+        stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
             ch.wait(seq[c])
@@ -484,8 +526,8 @@ class _PeerEpMlp(torch.autograd.Function):
                 backend.fp8_gmm(
                     act_fp8[r0:r1], fc2_w_fp8[j0:j1], sizes_cpu[j0:j1],
                     ms(_T.kInputGroup2, _M.kScaleInv, j0), ms(_T.kWeightGroup2, _M.kScaleInv, j0),
-                    c=out_local[r0:r1], backward=False)
-            last = ch_back.push_arrays(_copy_blocks(out_np, plan.combine_arrays((j0, j1)), out_local.data_ptr(), row_bytes))
+                    c=out_local[r0:r1], backward=False, c_row_map=stage_map[r0:r1])
+            last = ch_back.push_arrays(_copy_blocks(out_np, stage_copies[(j0, j1)], out_local.data_ptr(), row_bytes))
         ch_back.wait(last)
         if grad_on:
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
@@ -558,6 +600,7 @@ class _PeerEpMlp(torch.autograd.Function):
         if dgrad:
             assert min(plan.gi_ids) >= 0, "input.requires_grad must agree on all ranks"
             gi_np = np.asarray([ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+        stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
             r0, r1 = cumsums[j0], cumsums[j1]
@@ -595,12 +638,12 @@ class _PeerEpMlp(torch.autograd.Function):
                 if dgrad:
                     backend.fp8_gmm(grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], sizes_cpu[j0:j1], dpre_si,
                                     ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=gi_local[r0:r1], backward=True,
-                                    b_is_kn=ctx.kn)
+                                    b_is_kn=ctx.kn, c_row_map=stage_map[r0:r1])
             elif wgrad:
                 grad_fc1[j0:j1].zero_()
                 grad_fc2[j0:j1].zero_()
             if dgrad:
-                last = ch_back.push_arrays(_copy_blocks(gi_np, plan.combine_arrays((j0, j1)), gi_local.data_ptr(), row_bytes))
+                last = ch_back.push_arrays(_copy_blocks(gi_np, stage_copies[(j0, j1)], gi_local.data_ptr(), row_bytes))
             else:
                 last = ch_back.push([])
             if live and need_t:

@@ -6,7 +6,7 @@ sm_90a.  The result, ``oracle/_ref/ref_fp8_gmm_kernels*.so``, is git-ignored but
 working tree to a GPU machine, where tests/test_gpu_vs_reference_kernels.py loads it as a byte-exact
 GPU-side oracle.  Takes several minutes (each translation unit includes torch/extension.h).
 
-Usage: python oracle/build_ref_kernels.py [/path/to/reference]
+Usage: python oracle/build_ref_kernels.py /path/to/reference     (or FP8GMM_REFERENCE_DIR=/path/to/reference)
 """
 import os
 import subprocess
@@ -18,7 +18,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FP8GMM_REFERENCE_DIR")
+    if not ref:
+        print("usage: python oracle/build_ref_kernels.py /path/to/reference   (or set FP8GMM_REFERENCE_DIR); nothing built")
+        return 0
     csrc = os.path.join(ref, "csrc")
     if not os.path.isdir(csrc):
         print(f"reference checkout not found at {ref}; nothing built")

@@ -48,6 +48,26 @@ def test_dispatch_then_combine_is_the_identity(P, E, chunks):
                 back[s][d:d + n] = recv[o][src:src + n]
     for s in range(P):
         assert (back[s] == x[s]).all()
+    # The staged form of the combine: the producing GEMM writes a chunk's rows source-major through its row map and
+    # one copy per (home rank, chunk) takes them home.  Must be the same permutation.
+    back2 = [np.full_like(x[s], -1) for s in range(P)]
+    for o in range(P):
+        row_map, copies = plans[o].staged_combine()
+        assert row_map.dtype == np.int32 and row_map.shape == (recv[o].shape[0],)
+        staged = np.full_like(recv[o], -1)
+        off = np.concatenate([[0], np.cumsum(plans[o].local_sizes)])
+        for j0, j1 in plans[o].chunks:
+            r0, r1 = int(off[j0]), int(off[j1])
+            rel = row_map[r0:r1]
+            assert sorted(rel.tolist()) == list(range(r1 - r0)), "the map permutes the rows of its chunk"
+            staged[r0 + rel] = recv[o][r0:r1]
+            homes, dst, src, n = copies[(j0, j1)]
+            assert sorted(homes.tolist()) == list(range(P)), "one copy per home rank and chunk"
+            for s, d, a, k in zip(homes.tolist(), dst.tolist(), src.tolist(), n.tolist()):
+                back2[s][d:d + k] = staged[a:a + k]
+        assert (staged != -1).all()
+    for s in range(P):
+        assert (back2[s] == x[s]).all()
 
 
 def test_chunks_cover_the_local_experts_once():

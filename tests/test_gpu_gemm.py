@@ -30,8 +30,8 @@ CASES = [
     # (group sizes, k, n, a dtype)                       what it covers
     ([16, 32, 16], 32, 64, E4),                          # the reference's GEMM fixture (fp8_gmm/test.py:172-175)
     ([16, 32, 16], 32, 64, E5),                          # its backward variant
-    ([128, 96, 160, 128], 512, 1024, E4),                # BASELINE config 1 forward
-    ([128, 96, 160, 128], 1024, 512, E5),                # BASELINE config 1 dgrad
+    ([128, 96, 160, 128], 512, 1024, E4),                # the CPU-runnable GroupedLinear configuration (E=4, K=512, N=1024), forward
+    ([128, 96, 160, 128], 1024, 512, E5),                # ... and its dgrad
     ([1, 0, 255, 129, 0, 7], 144, 272, E4),              # empty groups, ragged rows, K and N tails
     ([300, 5], 4096, 256, E4),                           # long K (32 pipeline wraps)
     ([4500], 128, 528, E5),                              # > 32 m-tiles: crosses a super-row of the tile order
@@ -126,7 +126,7 @@ def test_fused_activation_epilogue(cuda, act, sizes, k, n):
 
 
 WGRAD_CASES = [
-    ([128, 96, 160, 128], 1024, 512),     # BASELINE config 1
+    ([128, 96, 160, 128], 1024, 512),     # the CPU-runnable GroupedLinear configuration
     ([16, 32, 16], 64, 32),               # reference fixture sizes
     ([5, 0, 33, 130, 0, 1], 272, 144),    # padding to 16, empty groups -> zero gradients, ragged N / K tiles
     ([2000, 70], 128, 256),               # long contraction
@@ -214,7 +214,7 @@ def test_gemm_with_untransposed_weights_equals_the_transposed_path(cuda, sizes, 
 
 
 def test_mixtral_shaped_slice_properties(cuda):
-    """Full-size shapes (BASELINE config 2: hidden 4096, ffn 14336) on a slice the oracle cannot afford:
+    """Full-size shapes (the Mixtral-shaped MLP: hidden 4096, ffn 14336) on a slice the oracle cannot afford:
     checked through size-independent properties -- linearity in the per-group scales and agreement of a
     random sample of output elements with fp32 dot products of the dequantised operands."""
     from fp8_gmm_b200 import backend
@@ -243,3 +243,36 @@ def test_mixtral_shaped_slice_properties(cuda):
         ref = float(af[r].double() @ b[gg, cc].view(E4).float().double())
         got = float(c1[r, cc])
         assert abs(got - ref) <= 8e-3 * max(abs(ref), 64.0)
+
+
+@pytest.mark.parametrize("ctas", [0, 1])
+def test_row_mapped_output_equals_permuted_plain_output(cuda, ctas):
+    """c_row_map with a block permutation (runs of consecutive rows move together, as in the expert-parallel
+    exchange): slabs of 32 rows that stay consecutive leave through TMA stores at the mapped row, slabs that straddle
+    the end of a run through per-thread stores; either way row r of the product lands at row c_row_map[r], bit for
+    bit what the unmapped launch computes."""
+    from fp8_gmm_b200 import backend
+
+    sizes, k, n = [700, 0, 333, 1025], 256, 512
+    a, b, sa, sb = _operands(sizes, k, n, E4, seed=21)
+    m = sum(sizes)
+    g = torch.Generator().manual_seed(3)
+    cuts = sorted(set([0, m] + torch.randint(1, m, (14,), generator=g).tolist() + [32, 64, 96, 1000, 1032]))
+    runs = [(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1)]
+    order = torch.randperm(len(runs), generator=g).tolist()
+    row_map = torch.empty(m, dtype=torch.int32)
+    pos = 0
+    for i in order:                         # run i is placed at the next free position of the output
+        lo, hi = runs[i]
+        row_map[lo:hi] = torch.arange(pos, pos + hi - lo, dtype=torch.int32)
+        pos += hi - lo
+    try:
+        backend.set_gemm_variant(ctas=ctas)
+        plain = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda))
+        mapped = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda)
+        backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda), c=mapped, c_row_map=row_map.to(cuda))
+        backend.device_status()
+    finally:
+        backend.set_gemm_variant()
+    assert not torch.isnan(mapped.float()).any()
+    assert torch.equal(mapped[row_map.to(cuda).long()], plain)

@@ -182,7 +182,7 @@ def test_state_dict_round_trip_reproduces_fp8_state(cuda):
 
 
 def test_fine_grained_zipf_routing(cuda):
-    """BASELINE config 3 shapes (E=64, hidden 2048, ffn 1408, Zipf loads with empty and ragged groups) at a
+    """The fine-grained MoE shapes (E=64, hidden 2048, ffn 1408, Zipf loads with empty and ragged groups) at a
     reduced row count: outputs finite, empty experts get exactly zero weight gradients, and rows of
     each group depend only on that group's weights (zeroing another expert's weights changes nothing)."""
     import fp8_gmm_b200 as fg
