@@ -178,12 +178,25 @@ def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
         ectx = ep_peer.EpContext.setup(dev, model.group)
         channel = ectx.channel
         channel.wait_events = ectx.channel_back.wait_events = []   # one shared list, in program order
+        channel.round_events, ectx.channel_back.round_events = [], []
     timings = []
     backend.set_gemm_timings(timings)
     _timed(step, args.steps, world)
     backend.set_gemm_timings(None)
-    exposed_ms, last_step_waits = None, []
+    exposed_ms, last_step_waits, rounds = None, [], None
     if channel is not None:
+        # copy rounds of the last traced step on this rank: when each round started (ms after the first dispatch round
+        # of the step began), how long it took and at what rate it moved its bytes
+        def round_table(events):
+            per = len(events) // args.steps
+            last = events[-per:]
+            return [(round(first[0].elapsed_time(s), 2), round(s.elapsed_time(e), 2), round(b / max(s.elapsed_time(e), 1e-3) / 1e6, 1))
+                    for s, e, b in last]
+
+        first = channel.round_events[-(len(channel.round_events) // args.steps)]
+        rounds = {"dispatch_start_ms_dur_ms_GBps": round_table(channel.round_events),
+                  "combine_start_ms_dur_ms_GBps": round_table(ectx.channel_back.round_events)}
+        channel.round_events = ectx.channel_back.round_events = None
         exposed_ms = sum(s.elapsed_time(e) for s, e in channel.wait_events) / args.steps
         per_step = len(channel.wait_events) // args.steps
         last_step_waits = [round(s.elapsed_time(e), 3) for s, e in channel.wait_events[-per_step:]]
@@ -268,7 +281,8 @@ def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
                           # forward includes the host's wait for the size exchange; backward is pure enqueue time
                           "host_ms_per_step_by_rank": {"forward": [r[0] for r in per_rank], "backward": [r[1] for r in per_rank]},
                           "ms_per_step_waiting_for_rows_by_rank": [r[2] for r in per_rank],
-                          "waits_ms_last_step_by_rank": [r[3:] for r in per_rank]}
+                          "waits_ms_last_step_by_rank": [r[3:] for r in per_rank],
+                          "copy_rounds_last_step_rank0": rounds}
         if not args.no_cpu_baseline:
             cstep, cflops, desc = cpu_sample_step(H, F, wl["rows_per_expert"] * 8)
             ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)

@@ -109,6 +109,7 @@ class PeerChannel:
         self.side = [torch.cuda.Stream(device=device) for _ in range(max(copy_streams, 1) - 1)]
         self.seq = 0
         self.wait_events = None   # a list here collects (start, end) CUDA events around every wait (benchmarks)
+        self.round_events = None  # a list here collects (start, end, bytes) per round of copies on the copy stream
         arr = (ctypes.c_void_p * self.world)()
         for r in range(self.world):
             arr[r] = self.flags.ptrs[r] + 4 * self.rank       # my word in rank r's page
@@ -134,6 +135,10 @@ class PeerChannel:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
         base = arr.ctypes.data
         lanes = 1 + len(self.side) if n >= 2 * (1 + len(self.side)) else 1
+        trace = self.round_events
+        if trace is not None:
+            t_start = torch.cuda.Event(enable_timing=True)
+            t_start.record(self.stream)
         as_blocks = ctypes.POINTER(CopyBlock)
         if lanes == 1:
             check(lib.fp8gmm_peer_copy_blocks(ctypes.cast(base, as_blocks), n, self.stream.cuda_stream), "peer_copy_blocks")
@@ -151,6 +156,10 @@ class PeerChannel:
                                                       st.cuda_stream), "peer_copy_blocks")
             for st in self.side:
                 self.stream.wait_stream(st)
+        if trace is not None:
+            t_end = torch.cuda.Event(enable_timing=True)
+            t_end.record(self.stream)
+            trace.append((t_start, t_end, int(arr["bytes"].sum()) if n else 0))
         check(lib.fp8gmm_peer_signal(self._signal_targets, self.world, self.seq, self.stream.cuda_stream), "peer_signal")
         return self.seq
 
