@@ -50,8 +50,8 @@ import torch  # noqa: E402
 METRIC = "grouped_mlp_fwd_bwd_fp8_tflops"
 NOMINAL_FP8_TFLOPS = 4500.0
 # DRAM bytes (read + write) per GEMM launch, averaged over the six launches of one Mixtral-shaped step, from a
-# one-pass ncu capture of the six full-size launches (dram__bytes_read.sum + dram__bytes_write.sum: 17.10 GB in all).
-GEMM_DRAM_BYTES_PER_LAUNCH = 2.850e9
+# one-pass ncu capture of the six full-size launches (dram__bytes_read.sum + dram__bytes_write.sum: 17.76 GB in all).
+GEMM_DRAM_BYTES_PER_LAUNCH = 2.960e9
 
 # Expert-parallel workload (N > 1; weak scaling, the per-GPU work is fixed): 128 experts split evenly over the ranks,
 # hidden 4096, ffn 1536, SwiGLU, 32768 tokens per GPU routed top-8 (softmax over N(0,1) logits, 8 distinct experts per

@@ -82,6 +82,53 @@ def check_against_nccl_transport(fg, ep, model, args, wl, x_dev, dy_dev, sizes, 
     return "equal" if int(total) == 0 else f"{int(total)} tensors differ"
 
 
+def tensor_parallel_leg(fg, dev, world, steps):
+    """The reference's one collective at the Mixtral-shaped sizes: every rank holds a 1/world slice of the ffn
+    dimension of all 8 experts (fc1 column-parallel, fc2 row-parallel) and the same 32768 routed rows, so the input
+    gradient has to be summed over the ranks (GroupedMlp(..., has_tp=True)).  Timed three ways: without the sum, with
+    the chunked peer-memory reduction behind the fc1 data-gradient GEMM, and with the plain NCCL all-reduce."""
+    import fp8_gmm_b200.grouped_mlp as gm
+    from fp8_gmm_b200 import tp
+
+    E, H, F, rows = 8, 4096, 14336 // world, 32768
+    sizes = torch.full((E,), rows // E, dtype=torch.int64)
+    torch.manual_seed(5)
+    mlp = fg.GroupedMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu")
+    with torch.no_grad():
+        mlp.fc1_weight.normal_(0.0, 0.02)
+        mlp.fc2_weight.normal_(0.0, 0.02)
+    x = torch.randn(rows, H, device=dev).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+    recipe = fg.DelayedScaling(amax_history_len=16)
+
+    def make(has_tp):
+        def step():
+            mlp.fc1_weight.grad = mlp.fc2_weight.grad = x.grad = None
+            with fg.fp8_autocast(enabled=True, fp8_recipe=recipe):
+                out = mlp(x, sizes, has_tp=has_tp, tp_group=dist.group.WORLD if has_tp else None)
+            out.backward(dy)
+        return step
+
+    out = {}
+    saved = os.environ.get("FP8GMM_TP")
+    for name, has_tp, path in (("no_sum", False, None), ("peer_memory", True, "peer"), ("nccl_all_reduce", True, "nccl")):
+        if path is not None:
+            os.environ["FP8GMM_TP"] = path
+        step = make(has_tp)
+        for _ in range(3):
+            step()
+        out[name + "_ms_per_step"] = _timed(step, steps, world) / steps * 1e3
+    if saved is None:
+        os.environ.pop("FP8GMM_TP", None)
+    else:
+        os.environ["FP8GMM_TP"] = saved
+    out["exposed_ms_peer_memory"] = out["peer_memory_ms_per_step"] - out["no_sum_ms_per_step"]
+    out["exposed_ms_nccl_all_reduce"] = out["nccl_all_reduce_ms_per_step"] - out["no_sum_ms_per_step"]
+    out["workload"] = (f"Mixtral-shaped GroupedMlp, ffn 14336 split over {world} ranks, 32768 rows, grad_input "
+                       f"({rows} x {H} bf16 = {rows * H * 2 / 1e6:.0f} MB) summed over the ranks; {gm.TP_CHUNKS} chunks")
+    return out
+
+
 def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
     import fp8_gmm_b200 as fg
     from bench import E2EPipeline
@@ -233,6 +280,13 @@ def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
         check = check_against_nccl_transport(fg, ep, model, args, wl, x_dev, dy_dev, sizes, recipe, dev, world)
         backend.device_status()
 
+    tp_line = None
+    e2e_bytes = (e2e.h2d_bytes, e2e.d2h_bytes)
+    if world > 1:
+        del x_dev, dy_dev, e2e
+        torch.cuda.empty_cache()
+        tp_line = tensor_parallel_leg(fg, dev, world, args.steps)
+        backend.device_status()
     total_rows = torch.tensor([float(rows)], device=dev)
     if world > 1:
         dist.all_reduce(total_rows)
@@ -258,7 +312,7 @@ def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
             "frac_of_nominal_fp8_peak": value / (4500.0 * world),
             "clocks": clocks.summary(),
             "e2e": {"value": flops * args.steps / secs_e2e / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": e2e.h2d_bytes * world, "d2h_bytes_per_step": e2e.d2h_bytes * world,
+                    "h2d_bytes_per_step": e2e_bytes[0] * world, "d2h_bytes_per_step": e2e_bytes[1] * world,
                     "ms_per_step": secs_e2e / args.steps * 1e3,
                     "how": "per step and rank: tokens, output gradients, expert ids and router weights copied from pinned host "
                            "memory; sort / gather on the device (group sizes counted on the host from the same ids), "
@@ -283,6 +337,8 @@ def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
                           "ms_per_step_waiting_for_rows_by_rank": [r[2] for r in per_rank],
                           "waits_ms_last_step_by_rank": [r[3:] for r in per_rank],
                           "copy_rounds_last_step_rank0": rounds}
+        if tp_line is not None:
+            line["tp"] = tp_line
         if not args.no_cpu_baseline:
             cstep, cflops, desc = cpu_sample_step(H, F, wl["rows_per_expert"] * 8)
             ctf, _ = run_cpu(cstep, cflops, reps=3, warmup=1)

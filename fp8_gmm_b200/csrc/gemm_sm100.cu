@@ -79,6 +79,7 @@ struct GemmParams {
   int* status;
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
   unsigned long long wait_ns;  // limit of every mbarrier wait (fp8gmm_set_wait_limits)
+  unsigned int* wave_counter;  // long contractions: tiles started so far (zeroed before the launch), or NULL
   int b_mn;            // kModeRows only: B is (G, K, N) row-major, read MN-major through the 3-D map_b (x = n, y = k, z = group)
   int mn_major;        // kModeWgrad only: operands are row-major (rows x features) slices, i.e. MN-major for the MMA
   int super_tiles;     // m-tiles per super-row of the tile order (see decode_tile)
@@ -148,6 +149,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, code, limit_ns);
+}
+
+// Soft wave barrier for long contractions.  The tiles that run side by side share operand boxes through L2 (an A box
+// is read by every n-tile in flight, a B box by every m-tile of the super-row), which only works while they sweep the
+// contraction in step.  With a contraction of 14336 or 28672 a tile takes ~100 us, the CTA pairs drift apart by more
+// than L2 can bridge, and DRAM reads grow to several times the operand bytes.  So before its first load of a tile the
+// leader's producer counts itself in and waits until every tile of the same wave has been started -- for at most
+// kWaveWaitNs: this is a hint, not a dependency, and a pair that is late (or not yet resident) is simply not waited for.
+constexpr unsigned long long kWaveWaitNs = 20000ull;
+__device__ __forceinline__ void wave_arrive_and_wait(unsigned int* counter, unsigned int target) {
+  atomicAdd(counter, 1u);
+  const unsigned long long t0 = global_ns();
+  while (*reinterpret_cast<volatile unsigned int*>(counter) < target) {
+    if (global_ns() - t0 > kWaveWaitNs) break;
+    __nanosleep(100);
+  }
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
@@ -449,6 +466,10 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
       const uint32_t full0_leader = kCtas == 2 ? map_to_cta(full_bar(0), 0) : 0;
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
         const TileInfo t = decode_tile<kCtas>(p, tile, rank);
+        if (p.wave_counter != nullptr && leader) {
+          const int wave_end = (tile / num_workers + 1) * num_workers;
+          wave_arrive_and_wait(p.wave_counter, static_cast<unsigned int>(min(wave_end, p.total_tiles)));
+        }
         const CUtensorMap* map_a = p.mode == kModeRows ? &p.map_a : &p.maps[2 * t.group];
         const CUtensorMap* map_b = p.mode == kModeRows ? &p.map_b : &p.maps[2 * t.group + 1];
         if (p.mode == kModeWgrad && t.group != acquired_group && t.num_kb > 0) {
@@ -908,6 +929,7 @@ struct Tuning {
   bool tma_epilogue = true; // full 32-row slabs leave through shared memory + TMA stores
   int super_rows_short = kSuperRowsShortK;  // rows per super-row of the tile order, contraction <= kLongK
   int super_rows_long = kSuperRowsLongK;    // ... and above (FP8GMM_GEMM_SUPER_ROWS=short,long; multiples of 256)
+  bool wave_sync = true;                    // soft wave barrier for long contractions (FP8GMM_GEMM_WAVE_SYNC=0 turns it off)
 };
 Tuning& tuning() {
   static Tuning t = [] {
@@ -917,6 +939,8 @@ Tuning& tuning() {
     e = getenv("FP8GMM_GEMM_EPILOGUE");
     v.tma_epilogue = !(e != nullptr && e[0] == 'd');
     v.tail_split = getenv("FP8GMM_GEMM_NO_TAIL_SPLIT") == nullptr;
+    e = getenv("FP8GMM_GEMM_WAVE_SYNC");
+    v.wave_sync = !(e != nullptr && e[0] == '0');
     e = getenv("FP8GMM_GEMM_SUPER_ROWS");
     int a = 0, b = 0;
     if (e != nullptr && sscanf(e, "%d,%d", &a, &b) == 2 && a >= 256 && b >= 256 && a % 256 == 0 && b % 256 == 0) {
@@ -946,6 +970,33 @@ uint32_t make_idesc(int a_format, int b_format, int ctas, bool a_mn = false, boo
 // fills every SM is delayed as a whole when another kernel (an NCCL exchange on a second stream) holds a few SMs.
 int g_sm_limit = 0;
 
+// Wave counters of the long-contraction launches: a small ring of words in device memory, one per launch in flight.
+constexpr int kWaveSlots = 64;
+__device__ unsigned int g_wave_counters[kWaveSlots];
+unsigned int* g_wave_addr[64] = {nullptr};
+std::mutex g_wave_mutex;
+unsigned int g_wave_next = 0;
+
+// Zeroes the next counter on `s` and returns its device address (NULL if the symbol cannot be resolved: no barrier).
+unsigned int* next_wave_counter(cudaStream_t s) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  unsigned int* base;
+  unsigned int slot;
+  {
+    std::lock_guard<std::mutex> lock(g_wave_mutex);
+    if (g_wave_addr[dev] == nullptr) {
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_wave_counters) != cudaSuccess) return nullptr;
+      g_wave_addr[dev] = static_cast<unsigned int*>(ptr);
+    }
+    base = g_wave_addr[dev];
+    slot = g_wave_next++ % kWaveSlots;
+  }
+  if (cudaMemsetAsync(base + slot, 0, sizeof(unsigned int), s) != cudaSuccess) return nullptr;
+  return base + slot;
+}
+
 int launch(GemmParams& p, int ctas, cudaStream_t s) {
   // The attribute is per device and the call is idempotent and cheap, so it is simply repeated.
   int sms = sm_count();
@@ -953,6 +1004,7 @@ int launch(GemmParams& p, int ctas, cudaStream_t s) {
   const int workers = sms / ctas > 0 ? sms / ctas : 1;
   const int grid = ctas * (p.total_tiles < workers ? p.total_tiles : workers);
   p.wait_ns = gemm_wait_limit_ns();
+  p.wave_counter = (p.mode == kModeRows && p.k > kLongK && tuning().wave_sync && p.total_tiles > workers) ? next_wave_counter(s) : nullptr;
   if (ctas == 2) {
     FP8GMM_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::kSmemBytes));
     grouped_gemm_pair_kernel<<<grid, kThreads, Cfg<2>::kSmemBytes, s>>>(p);
