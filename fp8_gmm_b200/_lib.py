@@ -110,6 +110,7 @@ SYMBOLS = {
     "fp8gmm_peer_open": (ctypes.c_int, [c_vp, ctypes.POINTER(c_vp)]),
     "fp8gmm_peer_close": (ctypes.c_int, [c_vp]),
     "fp8gmm_peer_copy_blocks": (ctypes.c_int, [ctypes.POINTER(CopyBlock), ctypes.c_int, c_vp]),
+    "fp8gmm_block_permute_rows": (ctypes.c_int, [c_vp, c_vp, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_i64, c_i64, c_vp]),
     "fp8gmm_peer_signal": (ctypes.c_int, [ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_uint32, c_vp]),
     "fp8gmm_peer_wait": (ctypes.c_int, [c_vp, ctypes.c_int, ctypes.c_uint32, c_vp]),
     "fp8gmm_peer_reduce_scatter_bf16": (ctypes.c_int, [ctypes.POINTER(c_vp), ctypes.c_int, ctypes.c_int, c_i64, c_i64, ctypes.c_int, c_vp]),

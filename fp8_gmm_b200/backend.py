@@ -357,6 +357,21 @@ def blocked_cast(inp, out, perm, scale, amax, num_groups):
         a.scatter()
 
 
+def block_permute_rows(src, dst, src_start, dst_start, rows):
+    """Block permutation of rows between two tensors of equal row width: block b = ``rows[b]`` consecutive rows from
+    row ``src_start[b]`` of ``src`` to row ``dst_start[b]`` of ``dst`` (host int64 sequences); see
+    fp8gmm_block_permute_rows."""
+    _require(src.is_cuda and dst.is_cuda and src.is_contiguous() and dst.is_contiguous(), "block_permute_rows: contiguous CUDA tensors")
+    _require(src.dim() == 2 and dst.dim() == 2 and src.shape[1] == dst.shape[1] and src.dtype == dst.dtype,
+             "block_permute_rows: tensors must be 2-D with the same row width and dtype")
+    a, k1 = _i64_array(src_start)
+    b, k2 = _i64_array(dst_start)
+    n, k3 = _i64_array(rows)
+    check(lib.fp8gmm_block_permute_rows(src.data_ptr(), dst.data_ptr(), a, b, n, len(rows), src.shape[1] * src.element_size(),
+                                        _stream()), "block_permute_rows")
+    del k1, k2, k3
+
+
 def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None, b_layout=0):
     args = GemmArgs()
     args.a, args.b, args.c = a.data_ptr(), b3.data_ptr(), c.data_ptr()

@@ -67,6 +67,50 @@ __global__ void peer_wait_kernel(const uint32_t* flags, int count, uint32_t valu
 }
 
 // ---------------------------------------------------------------------------------------------
+// Block permutation of rows in local memory (HBM-bound).  The expert-parallel forward receives a chunk's rows
+// source-major (one large copy per sending rank) and the grouped GEMM wants them expert-major; the rows have to be
+// copied out of the receive buffer once anyway (the fc1 weight gradient needs them after the buffer has been reused),
+// so that copy applies the permutation.  Blocks are runs of consecutive rows; a CTA takes 32 KB pieces of the
+// concatenated blocks, 16-byte vectors, eight loads in flight per thread.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPermMaxBlocks = 160;   // per launch (the parameter block stays below 4 KB)
+constexpr int kPermUnroll = 8;
+
+struct PermParams {
+  const uint8_t* src[kPermMaxBlocks];
+  uint8_t* dst[kPermMaxBlocks];
+  unsigned int vec_start[kPermMaxBlocks + 1];   // prefix sums of the blocks' 16-byte vector counts
+  int count;
+};
+
+__global__ void __launch_bounds__(256) block_permute_kernel(const __grid_constant__ PermParams p) {
+  const unsigned int total = p.vec_start[p.count];
+  const unsigned int per_piece = 256u * kPermUnroll;
+  const unsigned int pieces = (total + per_piece - 1) / per_piece;
+  for (unsigned int c = blockIdx.x; c < pieces; c += gridDim.x) {
+    const unsigned int base = c * per_piece;
+    int b = upper_slot(reinterpret_cast<const int*>(p.vec_start), p.count, static_cast<int>(base));
+    uint4 v[kPermUnroll];
+    int blk[kPermUnroll];
+#pragma unroll
+    for (int u = 0; u < kPermUnroll; ++u) {
+      const unsigned int i = base + u * 256u + threadIdx.x;
+      blk[u] = -1;
+      if (i < total) {
+        while (i >= p.vec_start[b + 1]) ++b;
+        blk[u] = b;
+        v[u] = ld_stream16(p.src[b] + static_cast<size_t>(i - p.vec_start[b]) * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPermUnroll; ++u) {
+      const unsigned int i = base + u * 256u + threadIdx.x;
+      if (blk[u] >= 0) *reinterpret_cast<uint4*>(p.dst[blk[u]] + static_cast<size_t>(i - p.vec_start[blk[u]]) * 16) = v[u];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Sum of a bf16 buffer over the ranks of a tensor-parallel group, over peer memory (plain peer loads; no
 // multimem, no TMA).  The reference all-reduces the input gradient of its MLP with NCCL after the fc1 data-gradient
 // GEMM (fp8_gmm/grouped_mlp.py:300-303,323-324); here the GEMM writes its partial rows into a peer-mapped staging
@@ -255,6 +299,44 @@ int fp8gmm_peer_copy_blocks(const fp8gmm_copy_block* blocks, int count, void* st
     FP8GMM_CHECK_CUDA(cudaMemcpyAsync(blocks[i].dst, blocks[i].src, blocks[i].bytes, cudaMemcpyDeviceToDevice, s));
   }
   return FP8GMM_OK;
+}
+
+int fp8gmm_block_permute_rows(const void* src, void* dst, const int64_t* src_start, const int64_t* dst_start,
+                              const int64_t* rows, int64_t num_blocks, int64_t row_bytes, void* stream) {
+  using namespace fp8gmm;
+  FP8GMM_CHECK_ARG(num_blocks >= 0 && row_bytes > 0 && row_bytes % 16 == 0, "block_permute_rows: row_bytes must be a positive multiple of 16");
+  if (num_blocks == 0) return FP8GMM_OK;
+  FP8GMM_CHECK_ARG(src && dst && src_start && dst_start && rows, "block_permute_rows: NULL pointer");
+  FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0, "block_permute_rows: unaligned buffer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  PermParams p;
+  p.count = 0;
+  p.vec_start[0] = 0;
+  auto flush = [&]() -> int {
+    if (p.count == 0) return FP8GMM_OK;
+    const unsigned int pieces = (p.vec_start[p.count] + 256u * kPermUnroll - 1) / (256u * kPermUnroll);
+    const unsigned int cap = static_cast<unsigned int>(sm_count()) * 8u;
+    block_permute_kernel<<<static_cast<int>(pieces < cap ? pieces : cap), 256, 0, s>>>(p);
+    FP8GMM_CHECK_CUDA(cudaGetLastError());
+    count_launch();
+    p.count = 0;
+    return FP8GMM_OK;
+  };
+  for (int64_t i = 0; i < num_blocks; ++i) {
+    FP8GMM_CHECK_ARG(rows[i] >= 0 && src_start[i] >= 0 && dst_start[i] >= 0, "block_permute_rows: negative entry in block %lld", (long long)i);
+    if (rows[i] == 0) continue;
+    const uint64_t vecs = static_cast<uint64_t>(rows[i]) * static_cast<uint64_t>(row_bytes) / 16;
+    FP8GMM_CHECK_ARG(vecs <= 0x3FFFFFFFull, "block_permute_rows: block %lld is too large", (long long)i);
+    if (p.count == kPermMaxBlocks || static_cast<uint64_t>(p.vec_start[p.count]) + vecs > 0x7FFFFFFFull) {
+      const int rc = flush();
+      if (rc != FP8GMM_OK) return rc;
+    }
+    p.src[p.count] = static_cast<const uint8_t*>(src) + src_start[i] * row_bytes;
+    p.dst[p.count] = static_cast<uint8_t*>(dst) + dst_start[i] * row_bytes;
+    p.vec_start[p.count + 1] = p.vec_start[p.count] + static_cast<unsigned int>(vecs);
+    ++p.count;
+  }
+  return flush();
 }
 
 int fp8gmm_peer_signal(uint32_t* const* flags, int count, uint32_t value, void* stream) {

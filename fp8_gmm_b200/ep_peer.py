@@ -160,6 +160,37 @@ class PeerPlan:
             self._lists[key] = (row_map, copies)
         return self._lists[key]
 
+    def staged_dispatch(self):
+        """The same source-major-inside-the-chunk layout for the way in: a rank's rows for one owner and one chunk of
+        experts are one contiguous run at the source (rows are sorted by global expert), so with a source-major staging
+        buffer at the owner one copy per (owner, chunk) delivers them, and the owner brings them expert-major with a
+        local block permutation (fp8gmm_block_permute_rows).
+
+        Returns (copies, perms): ``copies[chunk]`` = four int64 arrays (owner, dst_row in the owner's staging buffer,
+        src_row here, rows), owners in the staggered order; ``perms[chunk]`` = three int64 arrays (staged start,
+        expert-major start, rows) of this rank's blocks (local expert, source) of the chunk."""
+        key = "stage_in"
+        if key not in self._lists:
+            El, r, P = self.experts_local, self.rank, self.world
+            by_all = self.by_owner.numpy()           # (owner, El, src)
+            exp_off = self.exp_off.numpy()           # (owner, El + 1)
+            blk_off = self.blk_off[r].numpy()        # (El, P)
+            send_off = self.send_off[r].numpy()      # (E + 1,)
+            order = np.asarray(self._peer_order(), dtype=np.int64)
+            copies, perms = {}, {}
+            for (j0, j1) in self.chunks:
+                cnt_all = by_all[:, j0:j1, :]                                  # (owner, jc, src)
+                per_src = cnt_all.sum(1)                                       # (owner, src)
+                src_base = np.cumsum(per_src, 1) - per_src                     # rows of earlier sources in the chunk
+                dst_row = exp_off[order, j0] + src_base[order, r]
+                copies[(j0, j1)] = (order, dst_row, send_off[order * El + j0], per_src[order, r])
+                cnt = cnt_all[r]                                               # (jc, src) at this owner
+                staged = int(exp_off[r, j0]) + src_base[r][None, :] + (np.cumsum(cnt, 0) - cnt)
+                perms[(j0, j1)] = (np.ascontiguousarray(staged.reshape(-1)), np.ascontiguousarray(blk_off[j0:j1].reshape(-1)),
+                                   np.ascontiguousarray(cnt.reshape(-1)))
+            self._lists[key] = (copies, perms)
+        return self._lists[key]
+
     def staged_row_map(self, device):
         """The staged row map on the device (uploaded once per plan)."""
         key = ("stage_dev", device.index)
@@ -267,7 +298,7 @@ class EpContext:
         """Frees this context's peer buffers.  Collective: every rank calls it, with no exchange in flight."""
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
-        for buf in [self.recv, self._amax_stage] + self.pool.buffers:
+        for buf in [self.recv, self.recv_stage, self._amax_stage] + self.pool.buffers:
             if buf is not None:
                 buf.close()
         for ch in (self.channel, self.channel_back, self.ready):
@@ -303,6 +334,9 @@ class EpContext:
         self.host_group = host_group if host_group is not None else (dist.new_group(backend="gloo") if group is None else None)
         self.pool = _Pool(device, group)
         self.recv = None
+        self.recv_stage = None   # forward FP8 dispatch: source-major staging (one copy per sender and chunk lands here)
+        # FP8GMM_EP_DISPATCH=blocks keeps one copy per (owner, expert) straight into expert-major place in forward too
+        self.merged_dispatch = os.environ.get("FP8GMM_EP_DISPATCH", "merged") != "blocks"
         self._amax_stage = None
         self._amax_view = None
 
@@ -369,6 +403,10 @@ class EpContext:
                 dist.barrier(group=self.group)
                 self.recv.close()
             self.recv = PeerBuffer(int(plan.rows_local_max * 1.25) * row_bytes + 256, self.device, self.group)
+            if self.recv_stage is not None:
+                self.recv_stage.close()
+            # FP8 rows: half the bytes of the bf16-sized receive buffer
+            self.recv_stage = PeerBuffer(int(plan.rows_local_max * 1.25) * (row_bytes // 2) + 256, self.device, self.group)
         return plan
 
     def result_tensor(self, buf_id, rows, cols):
@@ -473,10 +511,20 @@ class _PeerEpMlp(torch.autograd.Function):
         x_ptr = src.data_ptr()
         recv_np = np.asarray(recv_ptrs, dtype=np.uint64)
 
+        # FP8 forward dispatch: one copy per (owner, chunk) into the owner's source-major staging buffer; the owner's
+        # block permutation (which is also the copy that keeps the rows for the fc1 weight gradient) puts them
+        # expert-major.  16-64 MiB copies instead of one 8 MiB copy per (owner, expert).
+        merged = fp8d and ectx.merged_dispatch
+        if merged:
+            stage_np = np.asarray(ectx.recv_stage.ptrs, dtype=np.uint64)
+            in_copies, in_perms = plan.staged_dispatch()
+
         def dispatch(chunk, first):
             extra = _amax_blocks(ectx, plan, amax_part, chunk) if fp8d else None
+            blocks = (_copy_blocks(stage_np, in_copies[chunk], x_ptr, d_bytes, extra) if merged else
+                      _copy_blocks(recv_np, plan.dispatch_arrays(chunk), x_ptr, d_bytes, extra))
             # later rounds do not wait for the compute stream: the rows they carry were ready before the first round
-            return ch.push_arrays(_copy_blocks(recv_np, plan.dispatch_arrays(chunk), x_ptr, d_bytes, extra), after_compute=first)
+            return ch.push_arrays(blocks, after_compute=first)
 
         # The first rounds are queued now (the rows are ready), the rest as the chunks before them are reached, so
         # that the copy engines see dispatch and combine rounds interleaved (EpContext.dispatch_ahead).
@@ -490,7 +538,12 @@ class _PeerEpMlp(torch.autograd.Function):
         fc2_w_fp8, fc2_w_t = cast_weight_cached(fc2_weight, fdt, (need_dgrad or need_wgrad) and not kn, ms(_T.kWeightGroup2, _M.kScale),
                                                 ms(_T.kWeightGroup2, _M.kAmax), cache, "fc2", reuse)
         keep_rows = need_wgrad and not need_t     # the row-major FP8 input is the fc1 wgrad operand: it must outlive forward
-        if fp8d:
+        if merged:
+            recv = None
+            staged_in = ectx.recv_stage.tensor((rows, hidden), fdt)
+            input_fp8 = torch.empty(rows, hidden, dtype=fdt, device=dev)     # expert-major, filled chunk by chunk
+            input_keep = input_fp8 if keep_rows else None
+        elif fp8d:
             # the received bytes are the GEMM operand as they lie in the receive buffer
             recv = None
             input_fp8 = ectx.recv.tensor((rows, hidden), fdt)
@@ -517,6 +570,8 @@ class _PeerEpMlp(torch.autograd.Function):
             if fp8d:
                 _merge_amax(ectx, plan, ms(_T.kInputGroup1, _M.kAmax, j0), (j0, j1))
             if r1 > r0:
+                if merged:
+                    backend.block_permute_rows(staged_in, input_fp8, *in_perms[(j0, j1)])
                 if not fp8d:
                     backend.grouped_cast_transpose(
                         recv[r0:r1], _rel(cumsums, j0, j1), input_fp8[r0:r1],
@@ -525,7 +580,7 @@ class _PeerEpMlp(torch.autograd.Function):
                 elif need_t:
                     backend.grouped_cast_transpose(input_fp8[r0:r1], _rel(cumsums, j0, j1), None,
                                                    input_t_fp8[offs[j0]:offs[j1]], _rel(offs, j0, j1), None, None)
-                elif keep_rows:
+                elif keep_rows and not merged:
                     # the receive buffer is reused by the next exchange: keep the rows for the fc1 weight gradient
                     input_keep[r0:r1].copy_(input_fp8[r0:r1])
                 backend.fp8_gmm(

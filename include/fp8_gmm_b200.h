@@ -407,6 +407,14 @@ typedef struct {
 /* Enqueues one device-to-device copy per block on `stream`, in order. */
 int fp8gmm_peer_copy_blocks(const fp8gmm_copy_block* blocks, int count, void* stream);
 
+/* Block permutation of rows in local memory: for every block b, `rows[b]` consecutive rows of `row_bytes` bytes (a
+ * multiple of 16) are copied from row src_start[b] of `src` to row dst_start[b] of `dst`.  The three arrays are HOST
+ * int64[num_blocks]; blocks must not overlap at the destination.  Used by the expert-parallel forward to bring rows
+ * that arrived source-major (one large copy per sending rank) into the expert-major order the grouped GEMM reads.
+ * No counterpart in the reference. */
+int fp8gmm_block_permute_rows(const void* src, void* dst, const int64_t* src_start, const int64_t* dst_start,
+                              const int64_t* rows, int64_t num_blocks, int64_t row_bytes, void* stream);
+
 /* One-warp kernel on `stream`: stores `value` to each of the `count` (<= 64) addresses in `flags` (host array of
  * device addresses, normally one word in every peer's memory; NULL entries are skipped) with system-scope
  * ordering after everything the stream did before. */

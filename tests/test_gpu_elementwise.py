@@ -210,3 +210,33 @@ def test_delayed_scaling_update_kernel(cuda):
             backend.delayed_scaling_update(d_h, d_s, d_i, 448.0, margin, algo)
             nh, ns, ni = O.delayed_scaling_update(hist, scale, 448.0, margin, algo)
             assert torch.equal(d_h.cpu(), nh) and torch.equal(d_s.cpu(), ns) and torch.equal(d_i.cpu(), ni)
+
+
+@pytest.mark.parametrize("width,dtype", [(4096, torch.float8_e4m3fn), (256, torch.bfloat16), (16, torch.uint8)])
+def test_block_permute_rows_moves_runs_of_rows(cuda, width, dtype):
+    """fp8gmm_block_permute_rows: runs of consecutive rows copied to new row positions (the expert-parallel forward
+    uses it to bring rows that arrived source-major into expert-major order).  Exact copy; rows outside every block
+    stay untouched; empty blocks and more blocks than one launch carries are handled."""
+    from fp8_gmm_b200 import backend
+
+    g = torch.Generator().manual_seed(width)
+    counts = torch.randint(0, 40, (200,), generator=g)
+    counts[5] = 0
+    total = int(counts.sum())
+    src_start = (torch.cumsum(counts, 0) - counts).tolist()
+    order = torch.randperm(len(counts), generator=g)
+    dst_start = torch.empty(len(counts), dtype=torch.int64)
+    pos = 3                                                     # three leading rows of dst belong to no block
+    for b in order.tolist():
+        dst_start[b] = pos
+        pos += int(counts[b])
+    raw = torch.randint(0, 256, (total, width * torch.empty((), dtype=dtype).element_size()), generator=g, dtype=torch.uint8)
+    src = raw.to(cuda).view(dtype)
+    dst = torch.full((total + 3, raw.shape[1]), 0x5A, dtype=torch.uint8, device=cuda).view(dtype)
+    backend.block_permute_rows(src, dst, src_start, dst_start.tolist(), counts.tolist())
+    backend.device_status()
+    got = dst.view(torch.uint8).cpu()
+    assert (got[:3] == 0x5A).all()
+    for b in range(len(counts)):
+        n = int(counts[b])
+        assert torch.equal(got[int(dst_start[b]):int(dst_start[b]) + n], raw[src_start[b]:src_start[b] + n])
