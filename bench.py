@@ -74,6 +74,7 @@ def parse():
     p.add_argument("--ep-transport", default="peer", choices=["peer", "nccl"],
                    help="expert-parallel leg: copy-engine pushes into peer memory pipelined with the GEMMs, or NCCL all-to-all")
     p.add_argument("--ep-bf16-dispatch", action="store_true", help="peer transport: dispatch rows as bf16 instead of FP8")
+    p.add_argument("--ep-quick", action="store_true", help="N > 1: timed step, traces and the local step only (no e2e, check, tp legs)")
     p.add_argument("--ep-chunks", default="tapered", help="expert chunks of the peer-transport pipeline: a count, 'tapered', "
                    "or comma-separated expert counts per chunk")
     return p.parse_args()
