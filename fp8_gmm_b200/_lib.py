@@ -48,6 +48,7 @@ class GemmArgs(ctypes.Structure):
         ("act_scale", c_fp), ("act_scale_stride", c_i64),
         ("act_amax", c_fp), ("act_amax_stride", c_i64),
         ("c_row_map", c_vp), ("b_layout", ctypes.c_int),
+        ("aux_in", c_vp), ("act_out_format", ctypes.c_int),
     ]
 
 

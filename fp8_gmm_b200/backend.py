@@ -28,7 +28,12 @@ WGRAD_ROWMAJOR = os.environ.get("FP8GMM_WGRAD", "rowmajor") != "transposed"
 # modules make no per-expert weight transposes either.  FP8GMM_DGRAD=transposed selects the reference's dataflow
 # (weights cast into (G, in, out) transposes, reference fp8_gmm/grouped_linear.py:70-73).
 DGRAD_KN = os.environ.get("FP8GMM_DGRAD", "kn") != "transposed"
-ACT_NONE, ACT_GELU, ACT_SWIGLU = 0, 1, 2
+# FP8GMM_FUSED_DSWIGLU=1 runs the SwiGLU backward in the epilogue of the fc2 data-gradient GEMM (fp8_gmm_dswiglu) whenever
+# no transposed copy of its result is wanted.  Off by default: on the Mixtral-shaped step the fused epilogue (one row
+# per thread, so its pre-activation loads do not coalesce) stretches that GEMM by more than the separate
+# activation-backward kernel costs (16.67-16.71 against 16.28-16.61 ms per step).
+FUSED_DSWIGLU = os.environ.get("FP8GMM_FUSED_DSWIGLU", "0") == "1"
+ACT_NONE, ACT_GELU, ACT_SWIGLU, ACT_DSWIGLU = 0, 1, 2, 3
 _ACT_CODE = {None: 0, "none": 0, "gelu": 1, "swiglu": 2}
 
 
@@ -372,9 +377,11 @@ def block_permute_rows(src, dst, src_start, dst_start, rows):
     del k1, k2, k3
 
 
-def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None, b_layout=0):
+def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None, b_layout=0, aux_in=None):
     args = GemmArgs()
-    args.a, args.b, args.c = a.data_ptr(), b3.data_ptr(), c.data_ptr()
+    args.a, args.b, args.c = a.data_ptr(), b3.data_ptr(), _ptr(c)
+    if aux_in is not None:
+        args.aux_in, args.act_out_format = aux_in.data_ptr(), _fp8_code(act_out.dtype)
     ms, keep = _i64_array(m_sizes)
     args.m_sizes = ms
     args.num_groups = num_groups
@@ -489,6 +496,30 @@ def fp8_gmm(
         _gemm(a, b, c, group_sizes, G, sa, sb, ACT_NONE, None, _Strided(None, 0), _Strided(None, 0), c_row_map,
               b_layout=1 if b_is_kn else 0)
     return c
+
+
+def fp8_gmm_dswiglu(dy, w, group_sizes, dy_scale_invs, w_scale_invs, pre_act, out, out_scales, out_amaxes, b_is_kn=False):
+    """fc2 data gradient with the SwiGLU backward fused in its epilogue, one launch:
+    ``d_act = (dy[rows of g] * sa[g]) (w[g] * sb[g])`` (rounded to bf16 as the plain GEMM stores it), then
+    ``out[rows of g] = fp8( dswiglu(d_act, pre_act) * out_scales[g] )`` = [d gate | d up] (sum m, 2F) with
+    ``out_amaxes[g]`` max-merged.  dy: (sum m, H) FP8; w: (G, F, H) FP8 K-major, or with ``b_is_kn`` the forward fc2
+    weights (G, H, F) as they are; pre_act: (sum m, 2F) bf16 = [gate | up].  Replaces fp8_gmm + the dswiglu cast kernel
+    (the d_act matrix never goes to memory).  Extension beyond the reference (GELU only there)."""
+    _cuda_2d(dy, "dy", _FP8)
+    _cuda_2d(w, "w", _FP8)
+    _cuda_2d(pre_act, "pre_act", (torch.bfloat16,))
+    _cuda_2d(out, "out", _FP8)
+    G = w.shape[0]
+    ffn = w.shape[2] if b_is_kn else w.shape[1]
+    _require(dy.dim() == 2 and w.dim() == 3 and dy.shape[1] == (w.shape[1] if b_is_kn else w.shape[2]),
+             "fp8_gmm_dswiglu: contraction dimensions differ")
+    _require(len(group_sizes) == G, "fp8_gmm_dswiglu: one group size per expert is required")
+    _require(tuple(pre_act.shape) == (dy.shape[0], 2 * ffn) and tuple(out.shape) == (dy.shape[0], 2 * ffn),
+             "fp8_gmm_dswiglu: pre_act and out must be (rows, 2 * ffn)")
+    sa, sb = _strided(dy_scale_invs, G), _strided(w_scale_invs, G)
+    _gemm(dy, w, None, group_sizes, G, sa, sb, ACT_DSWIGLU, out, _strided(out_scales, G),
+          _strided(out_amaxes, G, writable=True), b_layout=1 if b_is_kn else 0, aux_in=pre_act)
+    return out
 
 
 _workspaces = {}

@@ -69,6 +69,7 @@ struct GemmParams {
   const CUtensorMap* maps;    // kModeWgrad: [2g] = A_t,g (N, L_g), [2g+1] = B_t,g (K, L_g)
   uint16_t* c;
   uint8_t* act_out;
+  const uint16_t* aux_in;  // FP8GMM_ACT_DSWIGLU: bf16 pre-activation [gate | up], (sum m x 2n)
   const float* sa;
   const float* sb;
   const float* sc;
@@ -86,6 +87,7 @@ struct GemmParams {
   int tma_store;       // 1: full 32-row slabs of a tile leave through shared memory + TMA stores (map_c is valid)
   int mode;
   int activation;
+  int act_format;      // fp8 format of act_out (the forward activations are e4m3, the fused backward writes e5m2 or e4m3)
   int num_groups;
   int n;        // kModeRows: N (columns of C); kModeWgrad: K-dim of the weight (columns of C_g)
   int m_fixed;  // kModeWgrad: rows of every C_g (= N of the layer)
@@ -675,6 +677,75 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             }
           }
         }
+      } else if (p.activation == FP8GMM_ACT_DSWIGLU) {
+        // SwiGLU backward fused behind the fc2 data-gradient GEMM: the accumulator is d(act) for 256 columns of F;
+        // with the forward pre-activation [gate | up] of the same rows and columns it becomes d[gate | up], which is
+        // cast to fp8 with the group's scale and stored as the two halves of a (sum m x 2F) matrix, its amax merged.
+        // d(act) is rounded to bf16 first, so the values equal what the unfused path (bf16 GEMM output, then the
+        // activation-backward cast kernel) computes.  Row per thread: the pre-activation comes in as four 16-byte
+        // loads per half and step, issued before the accumulator is read.
+        const float sc = p.sc ? p.sc[t.group * p.sc_stride] : 1.f;
+        const int64_t ld_pre = 2 * static_cast<int64_t>(p.n);
+        const uint16_t* gate = p.aux_in + out_row * ld_pre + t.nt * kBlockN;
+        const uint16_t* up = gate + p.n;
+        uint8_t* dgate = p.act_out + out_row * p.ld_act + t.nt * kBlockN;
+        uint8_t* dup = dgate + p.n;
+        const bool e5 = p.act_format == FP8GMM_E5M2;
+        float amax = 0.f;
+        for (int c0 = 0; c0 < t.valid_cols; c0 += 32) {
+          uint4 pg[4], pu[4];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            pg[v] = pu[v] = make_uint4(0, 0, 0, 0);
+            if (row_ok && c0 + v * 8 < t.valid_cols) {
+              pg[v] = ld_stream16(gate + c0 + v * 8);
+              pu[v] = ld_stream16(up + c0 + v * 8);
+            }
+          }
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tc_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (c0 + v * 8 < t.valid_cols) {
+                const uint32_t gw[4] = {pg[v].x, pg[v].y, pg[v].z, pg[v].w};
+                const uint32_t uw[4] = {pu[v].x, pu[v].y, pu[v].z, pu[v].w};
+                float v0[8], v1[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  // one bf16 rounding of the de-scaled product, as the unfused GEMM output has
+                  const float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[v * 8 + j]) * alpha));
+                  const float y = (j & 1) ? bf16_hi(gw[j >> 1]) : bf16_lo(gw[j >> 1]);
+                  const float z = (j & 1) ? bf16_hi(uw[j >> 1]) : bf16_lo(uw[j >> 1]);
+                  const float sg = 1.f / (1.f + __expf(-y));
+                  v0[j] = x * z * (sg * (1.f + y * (1.f - sg)));
+                  v1[j] = x * (y * sg);
+                  amax = fmaxf(fabsf(v0[j]), amax);
+                  amax = fmaxf(fabsf(v1[j]), amax);
+                }
+                uint2 q0, q1;
+                if (e5) {
+                  q0 = make_uint2(cvt_fp8x4<FP8GMM_E5M2>(sc * v0[0], sc * v0[1], sc * v0[2], sc * v0[3]),
+                                  cvt_fp8x4<FP8GMM_E5M2>(sc * v0[4], sc * v0[5], sc * v0[6], sc * v0[7]));
+                  q1 = make_uint2(cvt_fp8x4<FP8GMM_E5M2>(sc * v1[0], sc * v1[1], sc * v1[2], sc * v1[3]),
+                                  cvt_fp8x4<FP8GMM_E5M2>(sc * v1[4], sc * v1[5], sc * v1[6], sc * v1[7]));
+                } else {
+                  q0 = make_uint2(cvt_fp8x4<FP8GMM_E4M3>(sc * v0[0], sc * v0[1], sc * v0[2], sc * v0[3]),
+                                  cvt_fp8x4<FP8GMM_E4M3>(sc * v0[4], sc * v0[5], sc * v0[6], sc * v0[7]));
+                  q1 = make_uint2(cvt_fp8x4<FP8GMM_E4M3>(sc * v1[0], sc * v1[1], sc * v1[2], sc * v1[3]),
+                                  cvt_fp8x4<FP8GMM_E4M3>(sc * v1[4], sc * v1[5], sc * v1[6], sc * v1[7]));
+                }
+                *reinterpret_cast<uint2*>(dgate + c0 + v * 8) = q0;
+                *reinterpret_cast<uint2*>(dup + c0 + v * 8) = q1;
+              }
+            }
+          }
+        }
+        if (p.amax) {
+          amax = warp_max(amax);
+          if (lane == 0) atomic_max_nonneg(p.amax + t.group * p.amax_stride, amax);
+        }
       } else if (p.activation == FP8GMM_ACT_GELU) {
         const float sc = p.sc ? p.sc[t.group * p.sc_stride] : 1.f;
         uint16_t* dst = p.c + out_row * p.ldc + t.nt * kBlockN;
@@ -1147,13 +1218,16 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   FP8GMM_CHECK_ARG(fmt_ok(a->a_format) && fmt_ok(a->b_format), "grouped_gemm: bad fp8 format");
   FP8GMM_CHECK_ARG(a->n > 0 && a->k > 0 && a->n % 16 == 0 && a->k % 16 == 0,
                    "grouped_gemm: N (%lld) and K (%lld) must be positive multiples of 16", (long long)a->n, (long long)a->k);
-  FP8GMM_CHECK_ARG(a->activation >= 0 && a->activation <= 2, "grouped_gemm: bad activation %d", a->activation);
+  FP8GMM_CHECK_ARG(a->activation >= 0 && a->activation <= 3, "grouped_gemm: bad activation %d", a->activation);
   if (a->num_groups == 0) return FP8GMM_OK;
   FP8GMM_CHECK_ARG(a->m_sizes != nullptr, "grouped_gemm: NULL m_sizes");
   FP8GMM_CHECK_ARG(a->a_scale_inv && a->b_scale_inv, "grouped_gemm: NULL scale_inv pointer");
   if (a->activation != FP8GMM_ACT_NONE) {
     FP8GMM_CHECK_ARG(a->act_out != nullptr, "grouped_gemm: activation requested without act_out");
     FP8GMM_CHECK_ARG(a->activation != FP8GMM_ACT_SWIGLU || a->n % 32 == 0, "grouped_gemm: SwiGLU needs N %% 32 == 0");
+    FP8GMM_CHECK_ARG(a->activation != FP8GMM_ACT_DSWIGLU || (a->aux_in != nullptr && fmt_ok(a->act_out_format) &&
+                                                           reinterpret_cast<uintptr_t>(a->aux_in) % 16 == 0),
+                     "grouped_gemm: the SwiGLU-backward epilogue needs a 16-byte aligned aux_in and a valid act_out_format");
   }
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -1195,7 +1269,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   }
   p.row_start[a->num_groups] = static_cast<int>(rows);
   if (rows == 0) return FP8GMM_OK;
-  FP8GMM_CHECK_ARG(a->a && a->b && a->c, "grouped_gemm: NULL operand pointer");
+  FP8GMM_CHECK_ARG(a->a && a->b && (a->c || a->activation == FP8GMM_ACT_DSWIGLU), "grouped_gemm: NULL operand pointer");
   FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a) | reinterpret_cast<uintptr_t>(a->b) |
                     reinterpret_cast<uintptr_t>(a->c) | reinterpret_cast<uintptr_t>(a->act_out)) % 16 == 0,
                    "grouped_gemm: operand pointers must be 16-byte aligned");
@@ -1203,7 +1277,8 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   int rc = encode_map(&p.map_a, a->a, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->k));
   if (rc != FP8GMM_OK) return rc;
   FP8GMM_CHECK_ARG(a->b_layout == 0 || a->b_layout == 1, "grouped_gemm: bad b_layout %d", a->b_layout);
-  FP8GMM_CHECK_ARG(a->b_layout == 0 || a->activation == FP8GMM_ACT_NONE, "grouped_gemm: b_layout 1 has no fused activation");
+  FP8GMM_CHECK_ARG(a->b_layout == 0 || a->activation == FP8GMM_ACT_NONE || a->activation == FP8GMM_ACT_DSWIGLU,
+                   "grouped_gemm: b_layout 1 has no fused forward activation");
   if (a->b_layout == 1)
     rc = encode_map_3d(&p.map_b, a->b, static_cast<uint64_t>(a->num_groups), static_cast<uint64_t>(a->k), static_cast<uint64_t>(a->n));
   else
@@ -1213,6 +1288,8 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.maps = nullptr;
   p.c = static_cast<uint16_t*>(a->c);
   p.act_out = static_cast<uint8_t*>(a->act_out);
+  p.aux_in = static_cast<const uint16_t*>(a->aux_in);
+  p.act_format = a->activation == FP8GMM_ACT_DSWIGLU ? a->act_out_format : FP8GMM_E4M3;
   FP8GMM_CHECK_ARG(a->c_row_map == nullptr || a->activation == FP8GMM_ACT_NONE,
                    "grouped_gemm: c_row_map is only supported without a fused activation");
   p.row_map = a->c_row_map;
@@ -1225,7 +1302,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.sc_stride = a->act_scale_stride;
   p.amax_stride = a->act_amax_stride;
   p.ldc = a->n;
-  p.ld_act = n_cols;
+  p.ld_act = a->activation == FP8GMM_ACT_DSWIGLU ? 2 * a->n : n_cols;
   p.status = device_status_word();
   FP8GMM_CHECK_ARG(p.status != nullptr, "grouped_gemm: cannot resolve the device status word");
   p.mode = kModeRows;
@@ -1238,7 +1315,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas, false, a->b_layout == 1);
   p.super_tiles = (a->k > kLongK ? tuning().super_rows_long : tuning().super_rows_short) / tile_m;
-  if (a->activation != FP8GMM_ACT_GELU && tuning().tma_epilogue) {
+  if (a->activation != FP8GMM_ACT_GELU && a->activation != FP8GMM_ACT_DSWIGLU && tuning().tma_epilogue) {
     rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
     if (rc != FP8GMM_OK) return rc;
     p.tma_store = 1;

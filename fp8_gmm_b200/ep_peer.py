@@ -697,12 +697,18 @@ class _PeerEpMlp(torch.autograd.Function):
                 elif wgrad:
                     backend.grouped_wgrad_rowmajor(grad_out_fp8[r0:r1], act_fp8[r0:r1], _rel(cumsums, j0, j1), dy_si,
                                                    ms(_T.kForwardInputGroup2, _M.kScaleInv, j0), c=grad_fc2[j0:j1])
-                grad_act = backend.fp8_gmm(grad_out_fp8[r0:r1], fc2_w_t[j0:j1], sizes_cpu[j0:j1], dy_si,
-                                           ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), backward=True, b_is_kn=ctx.kn)
-                backend.grouped_cast_transpose(
-                    grad_act, _rel(cumsums, j0, j1), grad_pre_fp8[r0:r1], grad_pre_t[t0:t1] if need_t else None,
-                    _rel(offs, j0, j1), ms(_T.kGradOutputGroup2, _M.kScale, j0), ms(_T.kGradOutputGroup2, _M.kAmax, j0),
-                    in2=pre_act[r0:r1], activation=activation)
+                if activation == "swiglu" and not need_t and backend.FUSED_DSWIGLU:
+                    backend.fp8_gmm_dswiglu(grad_out_fp8[r0:r1], fc2_w_t[j0:j1], sizes_cpu[j0:j1], dy_si,
+                                            ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), pre_act[r0:r1], grad_pre_fp8[r0:r1],
+                                            ms(_T.kGradOutputGroup2, _M.kScale, j0), ms(_T.kGradOutputGroup2, _M.kAmax, j0),
+                                            b_is_kn=ctx.kn)
+                else:
+                    grad_act = backend.fp8_gmm(grad_out_fp8[r0:r1], fc2_w_t[j0:j1], sizes_cpu[j0:j1], dy_si,
+                                               ms(_T.kForwardWeightGroup2, _M.kScaleInv, j0), backward=True, b_is_kn=ctx.kn)
+                    backend.grouped_cast_transpose(
+                        grad_act, _rel(cumsums, j0, j1), grad_pre_fp8[r0:r1], grad_pre_t[t0:t1] if need_t else None,
+                        _rel(offs, j0, j1), ms(_T.kGradOutputGroup2, _M.kScale, j0), ms(_T.kGradOutputGroup2, _M.kAmax, j0),
+                        in2=pre_act[r0:r1], activation=activation)
                 dpre_si = ms(_T.kGradOutputGroup2, _M.kScaleInv, j0)
                 if dgrad:
                     backend.fp8_gmm(grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], sizes_cpu[j0:j1], dpre_si,

@@ -131,16 +131,23 @@ class _GroupedMlp(torch.autograd.Function):
         elif wgrad:
             grad_fc2_weight = backend.grouped_wgrad_rowmajor(
                 grad_out_fp8, act_fp8, cumsums, dy_scale_inv, metas.get_meta_strided(_T.kForwardInputGroup2, _M.kScaleInv))
-        grad_act = backend.fp8_gmm(
-            grad_out_fp8, fc2_w_t, group_sizes, dy_scale_inv,
-            metas.get_meta_strided(_T.kForwardWeightGroup2, _M.kScaleInv), backward=True, b_is_kn=ctx.kn)
-        # d(activation) fused with the e5m2 cast, the padded transpose and the amax
         grad_pre_fp8 = torch.empty(pre_act.shape, dtype=g_dtype, device=dev)
         grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=g_dtype, device=dev) if need_t else None
-        backend.grouped_cast_transpose(
-            grad_act, cumsums, grad_pre_fp8, grad_pre_t, offs,
-            metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScale), metas.get_meta_strided(_T.kGradOutputGroup2, _M.kAmax),
-            in2=pre_act, activation=ctx.activation)
+        dpre_scale, dpre_amax = (metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScale),
+                                 metas.get_meta_strided(_T.kGradOutputGroup2, _M.kAmax))
+        if ctx.activation == "swiglu" and not need_t and backend.FUSED_DSWIGLU:
+            # fc2 dgrad with the SwiGLU backward, the cast and the amax in its epilogue: d(act) never goes to memory
+            backend.fp8_gmm_dswiglu(
+                grad_out_fp8, fc2_w_t, group_sizes, dy_scale_inv,
+                metas.get_meta_strided(_T.kForwardWeightGroup2, _M.kScaleInv), pre_act, grad_pre_fp8, dpre_scale, dpre_amax,
+                b_is_kn=ctx.kn)
+        else:
+            grad_act = backend.fp8_gmm(
+                grad_out_fp8, fc2_w_t, group_sizes, dy_scale_inv,
+                metas.get_meta_strided(_T.kForwardWeightGroup2, _M.kScaleInv), backward=True, b_is_kn=ctx.kn)
+            # d(activation) fused with the e5m2 cast, the padded transpose and the amax
+            backend.grouped_cast_transpose(
+                grad_act, cumsums, grad_pre_fp8, grad_pre_t, offs, dpre_scale, dpre_amax, in2=pre_act, activation=ctx.activation)
         dpre_scale_inv = metas.get_meta_strided(_T.kGradOutputGroup2, _M.kScaleInv)
         grad_input, handle, reducer = None, None, None
         if ctx.input_requires_grad and ctx.has_tp and perm is None and tp.use_peer_reduction(ctx.tp_group):

@@ -37,7 +37,7 @@ typedef enum {
 
 typedef enum { FP8GMM_E4M3 = 0, FP8GMM_E5M2 = 1 } fp8gmm_format;
 
-typedef enum { FP8GMM_ACT_NONE = 0, FP8GMM_ACT_GELU = 1, FP8GMM_ACT_SWIGLU = 2 } fp8gmm_activation;
+typedef enum { FP8GMM_ACT_NONE = 0, FP8GMM_ACT_GELU = 1, FP8GMM_ACT_SWIGLU = 2, FP8GMM_ACT_DSWIGLU = 3 } fp8gmm_activation;
 
 /* Library version (major * 1000 + minor). */
 int fp8gmm_version(void);
@@ -211,6 +211,11 @@ int fp8gmm_blocked_cast(const fp8gmm_blocked_cast_args* args, void* stream);
  *   activation != NONE additionally writes act_out = e4m3( act(.) * act_scale[g] ) and merges
  *            max|act(.)| into act_amax[g]: GELU: act_out is (sum m x N); SWIGLU: b holds [gate rows |
  *            up rows] (N = 2F) and act_out is (sum m x N/2).
+ *            DSWIGLU (backward; no counterpart in the reference, which has GELU only and runs the
+ *            activation backward as a separate cast kernel, fp8_gmm/grouped_mlp.py:254-287): the product is
+ *            d(act) (sum m x N), rounded to bf16 as the plain epilogue would store it; with aux_in = the forward
+ *            pre-activation [gate | up] it becomes d[gate | up], written as act_out = fp8(. * act_scale[g])
+ *            (sum m x 2N, format act_out_format) with max|.| merged into act_amax[g].  c is not written and may be NULL.
  * N and K must be multiples of 16 (the reference assumes the same: fp8_gmm/grouped_linear.py:69).
  * Replaces Fp8GroupedGemm + MultiScaleMul (reference csrc/fp8_gmm.h:7-11, csrc/fp8_gmm.cu:163-205,
  * fp8_gmm/backend.py:78-82) and the per-group te_gemm loop with its GELU-aux epilogue (reference
@@ -243,7 +248,9 @@ typedef struct {
                                i.e. C_g = A_g B_g without a transpose: what dgrad needs with the forward weights
                                (G x out x in) as they are -- the tensor cores read B MN-major, so the per-expert
                                weight transposes of the reference (fp8_gmm/grouped_linear.py:70-73) are not needed.
-                               activation must be NONE. */
+                               activation must be NONE or DSWIGLU. */
+  const void* aux_in;       /* activation == DSWIGLU only: bf16 (sum m x 2N), the forward pre-activation [gate | up] */
+  int act_out_format;       /* activation == DSWIGLU only: fp8 format of act_out (the forward epilogues write E4M3) */
 } fp8gmm_gemm_args;
 
 int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* args, void* stream);

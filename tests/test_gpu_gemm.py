@@ -276,3 +276,47 @@ def test_row_mapped_output_equals_permuted_plain_output(cuda, ctas):
         backend.set_gemm_variant()
     assert not torch.isnan(mapped.float()).any()
     assert torch.equal(mapped[row_map.to(cuda).long()], plain)
+
+
+@pytest.mark.parametrize("sizes,k,f,b_is_kn", [([16, 32, 16], 32, 64, False), ([100, 0, 260, 3], 256, 384, True),
+                                               ([128, 96, 160, 128], 512, 1040, True), ([700, 1], 4096, 272, False)])
+@pytest.mark.parametrize("out_dtype", [E5, E4])
+def test_fused_dswiglu_epilogue_equals_gemm_then_cast_kernel(cuda, sizes, k, f, b_is_kn, out_dtype):
+    """fc2 data gradient with the SwiGLU backward in its epilogue against the two-kernel path it replaces (bf16 GEMM
+    output, then the activation-backward cast kernel): the same expressions on the same bf16-rounded values, so the
+    FP8 bytes are expected to be identical; the assertion allows one FP8 step on < 0.1 % of the elements in case the
+    two translation units contract multiply-adds differently.  The amax matches to 1e-6 relative.  Also against the
+    CPU oracle on the dequantised values."""
+    from fp8_gmm_b200 import backend
+
+    G, m = len(sizes), sum(sizes)
+    a, b, sa, sb = _operands(sizes, k, f, E5, seed=5 * k + f)          # b: (G, f, k)
+    pre = randn_bf16((m, 2 * f), 77)
+    scales = torch.linspace(3.0, 7.0, G)
+    d_a, d_sa, d_sb, d_pre, d_sc = a.to(cuda), sa.to(cuda), sb.to(cuda), pre.to(cuda), scales.to(cuda)
+    d_b = (b.view(torch.uint8).transpose(1, 2).contiguous().view(E4) if b_is_kn else b).to(cuda)
+    cums = [0]
+    for s_ in sizes:
+        cums.append(cums[-1] + s_)
+    fused = torch.full((m, 2 * f), 0x55, dtype=torch.uint8, device=cuda).view(out_dtype)
+    amax_f = torch.zeros(G, device=cuda)
+    backend.fp8_gmm_dswiglu(d_a, d_b, torch.tensor(sizes), d_sa, d_sb, d_pre, fused, d_sc, amax_f, b_is_kn=b_is_kn)
+    backend.device_status()
+    dact = backend.fp8_gmm(d_a, d_b, torch.tensor(sizes), d_sa, d_sb, backward=True, b_is_kn=b_is_kn)
+    two = torch.empty(m, 2 * f, dtype=out_dtype, device=cuda)
+    amax_t = torch.zeros(G, device=cuda)
+    backend.grouped_cast_transpose(dact, cums, two, None, None, (d_sc, 1), (amax_t, 1), in2=d_pre, activation="swiglu")
+    backend.device_status()
+    diff = fp8_steps(fused.cpu(), two.cpu())
+    assert int(diff.max()) <= 1 and float((diff != 0).float().mean()) < 1e-3
+    assert torch.allclose(amax_f, amax_t, rtol=1e-6, atol=0)
+    # oracle: d(act) rounded to bf16, SwiGLU backward in fp32, quantised per group
+    ref_dact = O.grouped_gemm(a, b, sizes, sa, sb)
+    ref = O.dswiglu(ref_dact.float(), pre.float())
+    start = 0
+    for g, s_ in enumerate(sizes):
+        if s_:
+            want = O.quantize(ref[start:start + s_], float(scales[g]), out_dtype)
+            got = fused[start:start + s_].cpu()
+            assert O.rel_frobenius(got.float(), want.float()) <= TOL
+        start += s_
