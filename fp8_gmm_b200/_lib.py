@@ -49,6 +49,7 @@ class GemmArgs(ctypes.Structure):
         ("act_amax", c_fp), ("act_amax_stride", c_i64),
         ("c_row_map", c_vp), ("b_layout", ctypes.c_int),
         ("aux_in", c_vp), ("act_out_format", ctypes.c_int),
+        ("c_peers", c_vp),
     ]
 
 

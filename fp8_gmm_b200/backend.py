@@ -377,7 +377,8 @@ def block_permute_rows(src, dst, src_start, dst_start, rows):
     del k1, k2, k3
 
 
-def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None, b_layout=0, aux_in=None):
+def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, c_row_map=None, b_layout=0, aux_in=None,
+          c_peers=None):
     args = GemmArgs()
     args.a, args.b, args.c = a.data_ptr(), b3.data_ptr(), _ptr(c)
     if aux_in is not None:
@@ -398,11 +399,23 @@ def _gemm(a, b3, c, m_sizes, num_groups, sa, sb, activation, act_out, sc, amax, 
         _require(c_row_map.is_cuda and c_row_map.dtype == torch.int32 and c_row_map.numel() == a.shape[0],
                  "c_row_map must be a CUDA int32 tensor with one entry per row of a")
         args.c_row_map = c_row_map.data_ptr()
+    if c_peers is not None:
+        _require(c_row_map is not None and c_peers.is_cuda and c_peers.dtype == torch.int64 and c_peers.is_contiguous(),
+                 "c_peers must be a CUDA int64 tensor of base addresses and needs a c_row_map")
+        args.c_peers = c_peers.data_ptr()
     with _Timed(2.0 * a.shape[0] * args.n * args.k):
         check(lib.fp8gmm_grouped_gemm(ctypes.byref(args), _stream()), "fp8_gmm")
     if amax.scatter:
         amax.scatter()
     del keep
+
+
+ROW_MAP_PEER_SHIFT = 26   # FP8GMM_ROW_MAP_PEER_SHIFT of the C header
+
+
+def peer_row_entry(rank, row):
+    """Row-map entry (works on ints and numpy arrays) naming row ``row`` of rank ``rank``'s buffer (see fp8_gmm, c_peers)."""
+    return (rank << ROW_MAP_PEER_SHIFT) | row
 
 
 def cublas_fp8_gemm(a, b, c, a_scale_inv, b_scale_inv, pre_gelu_out=None, c_scale=None, c_amax=None, backward=False):
@@ -450,6 +463,7 @@ def fp8_gmm(
     activation="gelu",
     c_row_map=None,
     b_is_kn=False,
+    c_peers=None,
 ):
     """Grouped GEMM ``c[rows of g] = (a[rows of g] * sa[g]) (b[g] * sb[g])^T`` in one launch.
 
@@ -462,6 +476,9 @@ def fp8_gmm(
     activation scaled by c_scales[g], c_amaxes[g] the amax.  activation="swiglu" expects b = [gate
     rows | up rows] (N = 2F) and produces a (sum m, F) ``c``.  ``c_row_map`` (CUDA int32, one entry per row
     of a; plain bf16 output only) makes the epilogue store row r of the product at row c_row_map[r] of c.
+    ``c_peers`` (CUDA int64: base addresses of one bf16 (rows, N) buffer per rank, peer-mapped) with a ``c_row_map``
+    whose entries are ``peer_row_entry(rank, row)``: the epilogue stores every row straight into the named rank's
+    buffer (expert parallelism: results leave for their home ranks without a copy); ``c`` must be None, None is returned.
     ``b_is_kn=True``: b is (G, K, N) row-major and ``c = a @ b[g]`` without a transpose -- dgrad with the forward weights
     (G, out, in) as they are (the tensor cores read B MN-major; no per-expert weight transposes needed).
     """
@@ -475,6 +492,12 @@ def fp8_gmm(
     fused = (c is not None and c.dtype in _FP8) or (c is None and c_dtype in _FP8)
     if fused and activation == "swiglu":
         n_out = b.shape[1] // 2
+    if c_peers is not None:
+        _require(c is None and not fused and c_row_map is not None, "fp8_gmm: c_peers takes the place of a plain bf16 c")
+        sa, sb = _strided(a_scale_invs, G), _strided(b_scale_invs, G)
+        _gemm(a, b, None, group_sizes, G, sa, sb, ACT_NONE, None, _Strided(None, 0), _Strided(None, 0), c_row_map,
+              b_layout=1 if b_is_kn else 0, c_peers=c_peers)
+        return None
     if c is None:
         c = torch.empty(a.shape[0], n_out, device=a.device, dtype=c_dtype)
     _require(tuple(c.shape) == (a.shape[0], n_out) and c.is_contiguous(), "fp8_gmm: bad output shape")

@@ -61,6 +61,9 @@ constexpr int kTmemCols = 512;
 constexpr int kMaxGroups = 512;
 
 enum GemmMode { kModeRows = 0, kModeWgrad = 1 };
+// Row map entries that name a destination rank (GemmParams::c_peers): rank in the bits from kPeerShift up, row below.
+constexpr int kPeerShift = FP8GMM_ROW_MAP_PEER_SHIFT;
+constexpr int kPeerRowMask = (1 << kPeerShift) - 1;
 
 struct GemmParams {
   CUtensorMap map_a;          // kModeRows: A (sum m, K)
@@ -79,6 +82,8 @@ struct GemmParams {
   int64_t ld_act;  // row pitch of act_out in bytes
   int* status;
   const int32_t* row_map;  // optional (plain epilogue, rows mode): output row r is stored at row row_map[r] of c
+  const unsigned long long* c_peers;  // optional, with row_map: base addresses of the ranks' result buffers; a map entry
+                                      // is then (rank << kPeerShift) | row and the row is stored in that rank's buffer
   unsigned long long wait_ns;  // limit of every mbarrier wait (fp8gmm_set_wait_limits)
   unsigned int* wave_counter;  // long contractions: tiles started so far (zeroed before the launch), or NULL
   int b_mn;            // kModeRows only: B is (G, K, N) row-major, read MN-major through the 3-D map_b (x = n, y = k, z = group)
@@ -208,6 +213,11 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void st_shared16(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
 }
 // Byte offset of 16-byte chunk `c` (0..7) of row `r` (0..31) inside a 4 KiB staging box with 128-byte rows in
 // the SWIZZLE_128B pattern the tensor map expects (the box starts on a 1024-byte boundary).
@@ -652,6 +662,69 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             if (lane == 0) {
               tma_store_2d(&p.map_c, box, col_base + c0 - 32, row_coord);
               bulk_commit();
+            }
+          }
+        }
+      } else if (p.activation == FP8GMM_ACT_NONE && p.c_peers != nullptr) {
+        // The rows leave for their home ranks from here: a map entry names the rank whose buffer takes the row and
+        // the row there, and the stores go straight into that rank's memory (plain 16-byte stores through the
+        // peer mapping; this rank's own rows take the same path into its own buffer).  A slab whose 32 rows stay
+        // consecutive at one destination is staged in shared memory, 64 columns at a time, and written as full
+        // 128-byte lines (eight lanes per row, four rows per instruction); a slab that straddles the end of a run
+        // of rows stores one row per thread.
+        const int entry = row_ok ? p.row_map[out_row] : -1;
+        const int first = __shfl_sync(0xFFFFFFFFu, entry, 0);
+        const bool slab = first >= 0 && t.valid_cols == kBlockN && __all_sync(0xFFFFFFFFu, entry == first + lane);
+        if (slab) {
+          uint16_t* base = reinterpret_cast<uint16_t*>(p.c_peers[first >> kPeerShift]) +
+                           static_cast<int64_t>(first & kPeerRowMask) * p.ldc + t.nt * kBlockN;
+          const int sub_row = lane >> 3, chunk = lane & 7;
+#pragma unroll 1
+          for (int c0 = 0; c0 < kBlockN; c0 += 64) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t r[32];
+              tmem_ld32(taddr + c0 + half * 32, r);
+              tc_wait_ld();
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
+                o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
+                o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
+                o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
+                st_shared16(stage0 + staged_chunk(lane, half * 4 + v), o);
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + sub_row;
+              const uint4 o = ld_shared16(stage0 + staged_chunk(rr, chunk));
+              *reinterpret_cast<uint4*>(base + static_cast<int64_t>(rr) * p.ldc + c0 + chunk * 8) = o;
+            }
+            __syncwarp();
+          }
+        } else {
+          uint16_t* dst = row_ok ? reinterpret_cast<uint16_t*>(p.c_peers[entry >> kPeerShift]) +
+                                       static_cast<int64_t>(entry & kPeerRowMask) * p.ldc + t.nt * kBlockN
+                                 : nullptr;
+          for (int c0 = 0; c0 < t.valid_cols; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c0, r);
+            tc_wait_ld();
+            if (row_ok) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (c0 + v * 8 < t.valid_cols) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * alpha, __uint_as_float(r[v * 8 + 1]) * alpha);
+                  o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * alpha, __uint_as_float(r[v * 8 + 3]) * alpha);
+                  o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * alpha, __uint_as_float(r[v * 8 + 5]) * alpha);
+                  o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * alpha, __uint_as_float(r[v * 8 + 7]) * alpha);
+                  *reinterpret_cast<uint4*>(dst + c0 + v * 8) = o;
+                }
+              }
             }
           }
         }
@@ -1269,7 +1342,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   }
   p.row_start[a->num_groups] = static_cast<int>(rows);
   if (rows == 0) return FP8GMM_OK;
-  FP8GMM_CHECK_ARG(a->a && a->b && (a->c || a->activation == FP8GMM_ACT_DSWIGLU), "grouped_gemm: NULL operand pointer");
+  FP8GMM_CHECK_ARG(a->a && a->b && (a->c || a->c_peers || a->activation == FP8GMM_ACT_DSWIGLU), "grouped_gemm: NULL operand pointer");
   FP8GMM_CHECK_ARG((reinterpret_cast<uintptr_t>(a->a) | reinterpret_cast<uintptr_t>(a->b) |
                     reinterpret_cast<uintptr_t>(a->c) | reinterpret_cast<uintptr_t>(a->act_out)) % 16 == 0,
                    "grouped_gemm: operand pointers must be 16-byte aligned");
@@ -1293,6 +1366,8 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   FP8GMM_CHECK_ARG(a->c_row_map == nullptr || a->activation == FP8GMM_ACT_NONE,
                    "grouped_gemm: c_row_map is only supported without a fused activation");
   p.row_map = a->c_row_map;
+  FP8GMM_CHECK_ARG(a->c_peers == nullptr || a->c_row_map != nullptr, "grouped_gemm: c_peers needs a c_row_map that names the ranks");
+  p.c_peers = reinterpret_cast<const unsigned long long*>(a->c_peers);
   p.sa = a->a_scale_inv;
   p.sb = a->b_scale_inv;
   p.sc = a->act_scale;
@@ -1315,7 +1390,7 @@ int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* a, void* stream) {
   p.total_tiles = static_cast<int>(tiles);
   p.idesc = make_idesc(a->a_format, a->b_format, ctas, false, a->b_layout == 1);
   p.super_tiles = (a->k > kLongK ? tuning().super_rows_long : tuning().super_rows_short) / tile_m;
-  if (a->activation != FP8GMM_ACT_GELU && a->activation != FP8GMM_ACT_DSWIGLU && tuning().tma_epilogue) {
+  if (a->activation != FP8GMM_ACT_GELU && a->activation != FP8GMM_ACT_DSWIGLU && a->c_peers == nullptr && tuning().tma_epilogue) {
     rc = encode_store_map(&p.map_c, a->c, static_cast<uint64_t>(rows), static_cast<uint64_t>(a->n));
     if (rc != FP8GMM_OK) return rc;
     p.tma_store = 1;

@@ -35,6 +35,7 @@ from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_s
 _T, _M = Fp8TensorType, MetaTensorType
 
 
+_DEFAULT_COMBINE = "staged"
 _TAPER = (1, 2, 4, 4, 3, 2)  # sixteenths of the local experts per chunk: small first and last rounds, which nothing hides
 
 
@@ -191,6 +192,30 @@ class PeerPlan:
             self._lists[key] = (copies, perms)
         return self._lists[key]
 
+    def direct_row_map(self):
+        """Row map for results that the GEMM epilogue stores straight into the home ranks' buffers: int32 numpy
+        (rows_local,), expert-major row here -> backend.peer_row_entry(home rank, row in the home rank's result tensor).
+        A home rank holds its rows sorted by global expert, so block (local expert j, source s) of this owner lands at
+        row send_off[s, first expert of this owner + j] there."""
+        key = "direct"
+        if key not in self._lists:
+            El, r, P = self.experts_local, self.rank, self.world
+            assert P <= 32 and self.rows_own_max < (1 << backend.ROW_MAP_PEER_SHIFT), "row-map entries hold 5 + 26 bits"
+            cnt = self.by_owner[r].numpy().reshape(-1)                          # blocks in expert-major order: (j, s)
+            start = self.blk_off[r].numpy().reshape(-1)
+            home_row = self.send_off.numpy()[:, r * El:(r + 1) * El].T.reshape(-1)    # (j, s) -> first row at home rank s
+            src = np.tile(np.arange(P, dtype=np.int64), El)
+            total = int(self.exp_off[r, -1])
+            entries = np.repeat(backend.peer_row_entry(src, home_row) - start, cnt) + np.arange(total, dtype=np.int64)
+            self._lists[key] = entries.astype(np.int32)
+        return self._lists[key]
+
+    def direct_row_map_dev(self, device):
+        key = ("direct_dev", device.index)
+        if key not in self._lists:
+            self._lists[key] = torch.from_numpy(self.direct_row_map()).to(device)
+        return self._lists[key]
+
     def staged_row_map(self, device):
         """The staged row map on the device (uploaded once per plan)."""
         key = ("stage_dev", device.index)
@@ -305,6 +330,7 @@ class EpContext:
             ch.close()
         self.recv = self._amax_stage = self._amax_view = None
         self.pool.buffers, self.pool.free = [], []
+        self._ptr_tables = {}
         self._instances.pop((self.device.index, id(self.group)), None)
 
     def __init__(self, device, group, host_group=None):
@@ -339,6 +365,26 @@ class EpContext:
         self.merged_dispatch = os.environ.get("FP8GMM_EP_DISPATCH", "merged") != "blocks"
         self._amax_stage = None
         self._amax_view = None
+        # How results go home.  "direct": the fc2 (forward) and fc1 data-gradient (backward) epilogues store every
+        # row straight into its home rank's result tensor through the peer mapping, so the combine exchange is part
+        # of the GEMM and a round is only a signal.  "staged": the epilogue writes a local source-major staging
+        # buffer and the copy engines take one block per (home rank, chunk) home.
+        self.direct_combine = os.environ.get("FP8GMM_EP_COMBINE", _DEFAULT_COMBINE) == "direct"
+        self._ptr_tables = {}
+
+    def result_ptr_table(self, buf_ids):
+        """Device int64 vector: address, in this rank's address space, of rank r's result buffer buf_ids[r]."""
+        key = tuple(buf_ids)
+        if key not in self._ptr_tables:
+            ptrs = [self.pool.buffers[b].ptrs[r] for r, b in enumerate(buf_ids)]
+            self._ptr_tables[key] = torch.tensor(ptrs, dtype=torch.int64).to(self.device)
+        return self._ptr_tables[key]
+
+    def wait_buffers_free(self, plan):
+        """The compute stream waits until every rank has announced that its buffers of the step before are free (the
+        announcement plan() sent): needed before a kernel of this stream stores into other ranks' result tensors."""
+        check(lib.fp8gmm_peer_wait(self.ready.flags.local, self.world, plan.free_seq,
+                                   torch.cuda.current_stream(self.device).cuda_stream), "peer_wait")
 
     def amax_stage(self, experts_local):
         """(world x experts_local) fp32 in every rank's memory: row s = rank s's partial amaxes of my experts."""
@@ -395,6 +441,7 @@ class EpContext:
             if i not in mine:
                 pool.release(i)
         plan.out_ids, plan.gi_ids = [r[0] for r in resolved], [r[1] for r in resolved]
+        plan.free_seq = free_seq
         need = plan.rows_local_max * row_bytes
         if self.recv is None or self.recv.nbytes < need:
             # every rank sees the same sizes, so all of them take this branch together
@@ -555,12 +602,19 @@ class _PeerEpMlp(torch.autograd.Function):
         input_t_fp8 = torch.empty(offs[-1], hidden, dtype=fdt, device=dev) if need_t else None
         pre_act = torch.empty(rows, fc1_out, dtype=torch.bfloat16, device=dev)
         act_fp8 = torch.empty(rows, ffn, dtype=fdt, device=dev)
-        out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
         out = ectx.result_tensor(plan.out_ids[plan.rank], plan.rows_own, hidden)
-        out_np = np.asarray([ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
-        # results are written source-major inside each chunk by the fc2 epilogue, so one copy per (home rank, chunk)
-        # takes them home (blocks of tens of MiB instead of one block per expert: the copy engines run faster on them)
-        stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
+        direct = ectx.direct_combine
+        no_copies = np.empty(0, dtype=PeerChannel._BLOCK)
+        if direct:
+            # the fc2 epilogue stores every result row into its home rank's `out`: a combine round is only a signal
+            home_map, home_ptrs = plan.direct_row_map_dev(dev), ectx.result_ptr_table(plan.out_ids)
+            freed = False
+        else:
+            # results are written source-major inside each chunk by the fc2 epilogue, so one copy per (home rank, chunk)
+            # takes them home (blocks of tens of MiB instead of one block per expert: the copy engines run faster on them)
+            out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+            out_np = np.asarray([ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+            stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
             if c + ahead < len(chunks):
@@ -589,11 +643,16 @@ class _PeerEpMlp(torch.autograd.Function):
                     c=act_fp8[r0:r1], pre_gelu_out=pre_act[r0:r1],
                     c_scales=ms(_T.kInputGroup2, _M.kScale, j0), c_amaxes=ms(_T.kInputGroup2, _M.kAmax, j0),
                     backward=False, activation=activation)
+                if direct and not freed:
+                    ectx.wait_buffers_free(plan)
+                    freed = True
                 backend.fp8_gmm(
                     act_fp8[r0:r1], fc2_w_fp8[j0:j1], sizes_cpu[j0:j1],
                     ms(_T.kInputGroup2, _M.kScaleInv, j0), ms(_T.kWeightGroup2, _M.kScaleInv, j0),
-                    c=out_local[r0:r1], backward=False, c_row_map=stage_map[r0:r1])
-            last = ch_back.push_arrays(_copy_blocks(out_np, stage_copies[(j0, j1)], out_local.data_ptr(), row_bytes))
+                    c=None if direct else out_local[r0:r1], backward=False,
+                    c_row_map=home_map[r0:r1] if direct else stage_map[r0:r1], c_peers=home_ptrs if direct else None)
+            last = ch_back.push_arrays(no_copies if direct else
+                                       _copy_blocks(out_np, stage_copies[(j0, j1)], out_local.data_ptr(), row_bytes))
         ch_back.wait(last)
         if grad_on:
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
@@ -661,13 +720,21 @@ class _PeerEpMlp(torch.autograd.Function):
         grad_pre_t = torch.empty(offs[-1], fc1_out, dtype=gdt, device=dev) if need_t else None
         grad_fc1 = torch.empty(ctx.fc1_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
         grad_fc2 = torch.empty(ctx.fc2_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
-        gi_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev) if dgrad else None
         gi = ctx.gi
         ctx.gi = None
+        direct = ectx.direct_combine
+        no_copies = np.empty(0, dtype=PeerChannel._BLOCK)
+        gi_local = None
         if dgrad:
             assert min(plan.gi_ids) >= 0, "input.requires_grad must agree on all ranks"
-            gi_np = np.asarray([ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
-        stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
+            if direct:
+                # the gradient buffers were reserved (and announced free) together with the forward results: the
+                # compute stream has waited for that announcement in forward
+                home_map, home_ptrs = plan.direct_row_map_dev(dev), ectx.result_ptr_table(plan.gi_ids)
+            else:
+                gi_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
+                gi_np = np.asarray([ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+                stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
             r0, r1 = cumsums[j0], cumsums[j1]
@@ -712,13 +779,15 @@ class _PeerEpMlp(torch.autograd.Function):
                 dpre_si = ms(_T.kGradOutputGroup2, _M.kScaleInv, j0)
                 if dgrad:
                     backend.fp8_gmm(grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], sizes_cpu[j0:j1], dpre_si,
-                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=gi_local[r0:r1], backward=True,
-                                    b_is_kn=ctx.kn, c_row_map=stage_map[r0:r1])
+                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=None if direct else gi_local[r0:r1],
+                                    backward=True, b_is_kn=ctx.kn, c_row_map=home_map[r0:r1] if direct else stage_map[r0:r1],
+                                    c_peers=home_ptrs if direct else None)
             elif wgrad:
                 grad_fc1[j0:j1].zero_()
                 grad_fc2[j0:j1].zero_()
             if dgrad:
-                last = ch_back.push_arrays(_copy_blocks(gi_np, stage_copies[(j0, j1)], gi_local.data_ptr(), row_bytes))
+                last = ch_back.push_arrays(no_copies if direct else
+                                           _copy_blocks(gi_np, stage_copies[(j0, j1)], gi_local.data_ptr(), row_bytes))
             else:
                 last = ch_back.push([])
             if live and need_t:

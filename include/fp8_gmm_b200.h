@@ -201,6 +201,10 @@ int fp8gmm_blocked_cast(const fp8gmm_blocked_cast_args* args, void* stream);
  * Grouped GEMM (tensor-core bound): tcgen05 / TMEM kernel with TMA-fed FP8 tiles.
  * ---------------------------------------------------------------------------------------------- */
 
+/* Row-map entries that name a destination rank (fp8gmm_gemm_args.c_peers): the rank sits in the bits from this one up,
+ * the destination row in the bits below (so a destination buffer holds fewer than 2^26 rows, a group at most 32 ranks). */
+#define FP8GMM_ROW_MAP_PEER_SHIFT 26
+
 /*
  * Forward / dgrad:  C_g = act( (A_g B_g^T) * a_scale_inv[g] * b_scale_inv[g] )  for every group g.
  *   a        fp8 (sum m x K) row-major, groups are consecutive row blocks of m_sizes[g] rows
@@ -251,6 +255,14 @@ typedef struct {
                                activation must be NONE or DSWIGLU. */
   const void* aux_in;       /* activation == DSWIGLU only: bf16 (sum m x 2N), the forward pre-activation [gate | up] */
   int act_out_format;       /* activation == DSWIGLU only: fp8 format of act_out (the forward epilogues write E4M3) */
+  const void* const* c_peers; /* optional, needs c_row_map: device array of base addresses, one bf16 (rows x n) result
+                               buffer per rank of an expert-parallel group (peer-mapped memory of the other GPUs of
+                               the node, this GPU's own buffer at its own index).  A c_row_map entry is then
+                               (rank << FP8GMM_ROW_MAP_PEER_SHIFT) | row: the epilogue stores the row straight into
+                               that rank's buffer with plain stores, so the combine exchange needs no copy; `c` is
+                               not used and may be NULL.  The caller orders the launch after the owners of the
+                               buffers have released them and signals them after it (fp8gmm_peer_wait /
+                               fp8gmm_peer_signal). */
 } fp8gmm_gemm_args;
 
 int fp8gmm_grouped_gemm(const fp8gmm_gemm_args* args, void* stream);

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+from fp8_gmm_b200.backend import ROW_MAP_PEER_SHIFT
 from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds, resolve_result_buffers
 
 
@@ -68,6 +69,18 @@ def test_dispatch_then_combine_is_the_identity(P, E, chunks):
         assert (staged != -1).all()
     for s in range(P):
         assert (back2[s] == x[s]).all()
+    # The direct form: the producing GEMM's epilogue stores every row into its home rank's buffer through a row map
+    # whose entries name (home rank, row there).  Must be the same permutation again.
+    back3 = [np.full_like(x[s], -1) for s in range(P)]
+    for o in range(P):
+        entries = plans[o].direct_row_map()
+        assert entries.dtype == np.int32 and entries.shape == (recv[o].shape[0],) and (entries >= 0).all()
+        home, row = entries >> ROW_MAP_PEER_SHIFT, entries & ((1 << ROW_MAP_PEER_SHIFT) - 1)
+        for q in range(entries.size):
+            assert (back3[home[q]][row[q]] == -1).all(), "two rows land on the same home row"
+            back3[home[q]][row[q]] = recv[o][q]
+    for s in range(P):
+        assert (back3[s] == x[s]).all()
 
 
 def test_chunks_cover_the_local_experts_once():

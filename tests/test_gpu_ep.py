@@ -1,7 +1,8 @@
 """GPU, 2 ranks (skipped on a single-GPU machine): ExpertParallelMlp equals, bit for bit, one GroupedMlp that holds
 all experts on one GPU -- forward, backward, weight gradients and FP8 recipe state -- over two steps of delayed
-scaling, for the NCCL all-to-all transport and for the peer-memory transport with FP8 and with bf16 dispatch (the
-second step reuses the receive buffers and the result pool)."""
+scaling, for the NCCL all-to-all transport and for the peer-memory transport with FP8 and with bf16 dispatch, results
+going home through the GEMM epilogue's peer stores or through staged copies (the second step reuses the receive
+buffers and the result pool)."""
 import os
 
 import pytest
@@ -23,6 +24,10 @@ def _sizes(rank):
 def _worker(rank, port, errq, transport):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        if transport.startswith("peer"):
+            # how results go home: stored by the GEMM epilogue into the home rank's tensor, or staged + copy engines
+            os.environ["FP8GMM_EP_COMBINE"] = "staged" if transport.endswith("staged") else "direct"
+            transport = transport.replace("-staged", "")
         dev = torch.device("cuda", rank)
         torch.cuda.set_device(dev)
         dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
@@ -107,13 +112,13 @@ def _worker(rank, port, errq, transport):
         raise
 
 
-@pytest.mark.parametrize("transport", ["nccl", "peer", "peer-bf16"])
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer-bf16", "peer-staged", "peer-bf16-staged"])
 def test_expert_parallel_matches_single_gpu(cuda, transport):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs 2 GPUs")
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
-    port = 29900 + os.getpid() % 90 + {"nccl": 0, "peer": 100, "peer-bf16": 200}[transport]
+    port = 29900 + os.getpid() % 90 + {"nccl": 0, "peer": 100, "peer-bf16": 200, "peer-staged": 300, "peer-bf16-staged": 400}[transport]
     procs = [ctx.Process(target=_worker, args=(r, port, errq, transport)) for r in range(WORLD)]
     for p in procs:
         p.start()

@@ -278,6 +278,53 @@ def test_row_mapped_output_equals_permuted_plain_output(cuda, ctas):
     assert torch.equal(mapped[row_map.to(cuda).long()], plain)
 
 
+@pytest.mark.parametrize("ctas", [0, 1])
+@pytest.mark.parametrize("n", [512, 272])
+def test_rows_stored_into_named_buffers_equal_plain_output(cuda, ctas, n):
+    """c_peers: the row map names (buffer, row) and the epilogue stores each row into that buffer -- the expert-parallel
+    combine with the home ranks' result tensors as buffers.  Here the "ranks" are three tensors on this GPU; runs of
+    rows move together, some a multiple of 32 long (shared-memory staged 128-byte line stores), some not (one row per
+    thread), and n = 272 leaves a ragged last column tile.  Every row must land bit for bit where the map says and
+    nothing else may be written."""
+    from fp8_gmm_b200 import backend
+
+    sizes, k = [700, 0, 333, 1025], 256
+    a, b, sa, sb = _operands(sizes, k, n, E4, seed=22)
+    m = sum(sizes)
+    g = torch.Generator().manual_seed(5)
+    cuts = sorted(set([0, m] + torch.randint(1, m, (14,), generator=g).tolist() + [32, 64, 96, 1000, 1032]))
+    runs = [(cuts[i], cuts[i + 1]) for i in range(len(cuts) - 1)]
+    order = torch.randperm(len(runs), generator=g).tolist()
+    P = 3
+    fill = [5] * P                                   # first rows of every buffer stay untouched
+    buf_of = torch.empty(m, dtype=torch.int64)
+    row_of = torch.empty(m, dtype=torch.int64)
+    for idx, i in enumerate(order):
+        lo, hi = runs[i]
+        r = idx % P
+        buf_of[lo:hi] = r
+        row_of[lo:hi] = torch.arange(fill[r], fill[r] + hi - lo)
+        fill[r] += hi - lo
+    row_map = backend.peer_row_entry(buf_of, row_of).to(torch.int32)
+    bufs = [torch.full((fill[r] + 7, n), float("nan"), dtype=torch.bfloat16, device=cuda) for r in range(P)]
+    table = torch.tensor([t.data_ptr() for t in bufs], dtype=torch.int64).to(cuda)
+    try:
+        backend.set_gemm_variant(ctas=ctas)
+        plain = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda))
+        ret = backend.fp8_gmm(a.to(cuda), b.to(cuda), torch.tensor(sizes), sa.to(cuda), sb.to(cuda),
+                              c_row_map=row_map.to(cuda), c_peers=table)
+        backend.device_status()
+    finally:
+        backend.set_gemm_variant()
+    assert ret is None
+    for r in range(P):
+        mine = (buf_of == r).nonzero().flatten()
+        assert torch.equal(bufs[r][row_of[mine].to(cuda)], plain[mine.to(cuda)])
+        untouched = torch.ones(bufs[r].shape[0], dtype=torch.bool)
+        untouched[row_of[mine]] = False
+        assert torch.isnan(bufs[r][untouched.to(cuda)].float()).all()
+
+
 @pytest.mark.parametrize("sizes,k,f,b_is_kn", [([16, 32, 16], 32, 64, False), ([100, 0, 260, 3], 256, 384, True),
                                                ([128, 96, 160, 128], 512, 1040, True), ([700, 1], 4096, 272, False)])
 @pytest.mark.parametrize("out_dtype", [E5, E4])
