@@ -305,8 +305,8 @@ def run(args, metric, wl, peaks, ClockSampler, cpu_sample_step, run_cpu):
             "dtype": "fp8 (e4m3 fwd / e5m2 grad, fp32 accumulate in TMEM, bf16 out)", "data": "synthetic",
             "config": {"workload": wl["name"], "parallelism": f"ep{world}", "experts_per_gpu": E // world,
                        "exchange": (f"peer memory: {'bf16' if args.ep_bf16_dispatch else 'FP8'} dispatch pushed by the copy engines, bf16 combine "
-                                    + ("stored by the fc2 / fc1-dgrad GEMM epilogues straight into the home ranks' tensors, "
-                                       if ep_peer.EpContext.setup(dev, model.group).direct_combine else "staged and pushed by the copy engines, ")
+                                    + f"stored by the fc2 / fc1-dgrad GEMM epilogues straight into the tensors of home ranks {list(ep_peer.EpContext.setup(dev, model.group).direct_homes())} (rank 0's view), "
+                                    + "staged and pushed by the copy engines for the others, "
                                     + f"{args.ep_chunks} expert chunks pipelined with the GEMMs"
                                     if args.ep_transport == "peer" and world > 1 else "NCCL all-to-all" if world > 1 else "none"),
                        "routed_rows_per_gpu": TOKENS * TOPK,

@@ -35,7 +35,6 @@ from .utils import Fp8MetaWrapper, Fp8TensorType, MetaTensorType, cumsum_group_s
 _T, _M = Fp8TensorType, MetaTensorType
 
 
-_DEFAULT_COMBINE = "staged"
 _TAPER = (1, 2, 4, 4, 3, 2)  # sixteenths of the local experts per chunk: small first and last rounds, which nothing hides
 
 
@@ -210,10 +209,34 @@ class PeerPlan:
             self._lists[key] = entries.astype(np.int32)
         return self._lists[key]
 
-    def direct_row_map_dev(self, device):
-        key = ("direct_dev", device.index)
+    def combine_map(self, direct_homes):
+        """How this owner's result rows go home when the rows of the home ranks in ``direct_homes`` are stored by the
+        GEMM epilogue straight into those ranks' tensors and the others are staged source-major here and pushed by the
+        copy engines.  Returns (entries, copies): ``entries`` int32 numpy (rows_local,) for the epilogue -- a direct
+        row names (home rank, row there), a staged row names buffer index ``world`` (the local staging buffer, last in
+        the epilogue's table) and its staged row; ``copies[chunk]`` as in staged_combine, without the direct homes."""
+        key = ("mix", tuple(sorted(direct_homes)))
         if key not in self._lists:
-            self._lists[key] = torch.from_numpy(self.direct_row_map()).to(device)
+            rel, copies = self.staged_combine()
+            direct = self.direct_row_map().astype(np.int64)
+            exp_off = self.exp_off[self.rank].numpy()
+            chunk_start = np.zeros(rel.shape[0], dtype=np.int64)
+            for (j0, j1) in self.chunks:
+                chunk_start[int(exp_off[j0]):int(exp_off[j1])] = int(exp_off[j0])
+            homes = np.asarray(sorted(direct_homes), dtype=np.int64)
+            is_direct = np.isin(direct >> backend.ROW_MAP_PEER_SHIFT, homes)
+            entries = np.where(is_direct, direct, backend.peer_row_entry(self.world, chunk_start + rel)).astype(np.int32)
+            kept = {}
+            for chunk, arrays in copies.items():
+                mask = ~np.isin(arrays[0], homes)
+                kept[chunk] = tuple(np.ascontiguousarray(a[mask]) for a in arrays)
+            self._lists[key] = (entries, kept)
+        return self._lists[key]
+
+    def combine_map_dev(self, device, direct_homes):
+        key = ("mix_dev", device.index, tuple(sorted(direct_homes)))
+        if key not in self._lists:
+            self._lists[key] = torch.from_numpy(self.combine_map(direct_homes)[0]).to(device)
         return self._lists[key]
 
     def staged_row_map(self, device):
@@ -297,6 +320,17 @@ def resolve_result_buffers(picks, buffers_before):
     return missing, resolved
 
 
+def direct_homes_for(spec, rank, world):
+    """Home ranks served by the GEMM epilogue's peer stores for FP8GMM_EP_DIRECT = ``spec``: "all", "none", "auto" (all
+    in a group of two, none in larger groups) or a number k (this rank and the k ranks after it)."""
+    if spec == "auto":
+        spec = "all" if world <= 2 else "none"
+    if spec == "none":
+        return ()
+    k = world - 1 if spec == "all" else min(int(spec), world - 1)
+    return tuple(sorted((rank + i) % world for i in range(k + 1)))
+
+
 class EpContext:
     """Per (device, group) transport state shared by all ExpertParallelMlp modules: the channel (side stream and
     sequence numbers), the receive buffer for dispatched rows and the pool of result buffers.
@@ -330,7 +364,7 @@ class EpContext:
             ch.close()
         self.recv = self._amax_stage = self._amax_view = None
         self.pool.buffers, self.pool.free = [], []
-        self._ptr_tables = {}
+        self._ptr_tables, self._stage_out = {}, None
         self._instances.pop((self.device.index, id(self.group)), None)
 
     def __init__(self, device, group, host_group=None):
@@ -365,18 +399,37 @@ class EpContext:
         self.merged_dispatch = os.environ.get("FP8GMM_EP_DISPATCH", "merged") != "blocks"
         self._amax_stage = None
         self._amax_view = None
-        # How results go home.  "direct": the fc2 (forward) and fc1 data-gradient (backward) epilogues store every
-        # row straight into its home rank's result tensor through the peer mapping, so the combine exchange is part
-        # of the GEMM and a round is only a signal.  "staged": the epilogue writes a local source-major staging
-        # buffer and the copy engines take one block per (home rank, chunk) home.
-        self.direct_combine = os.environ.get("FP8GMM_EP_COMBINE", _DEFAULT_COMBINE) == "direct"
+        # How results go home.  The fc2 (forward) and fc1 data-gradient (backward) epilogues can store a row straight
+        # into its home rank's result tensor through the peer mapping (no copy, the exchange is part of the GEMM), or
+        # write it into a local source-major staging buffer from which the copy engines take one block per (home
+        # rank, chunk) home.  Peer stores stall the epilogue once the link is the bottleneck, staged rows cost the
+        # copy engines' time: FP8GMM_EP_DIRECT picks the home ranks served by peer stores -- "all", "none", a number
+        # k (this rank and the k ranks after it) or "auto": all in a group of two, where the rows of one GEMM cross the
+        # link faster than the GEMM computes them (17.1 against 18.4 ms per step); none in larger groups, where 3/4 and
+        # more of the rows leave (4 GPUs, one box: all 21.1 ms per step against 19.0 staged; own rows only 18.5-19.8,
+        # own + next rank 18.5, none 18.8-18.9: no gain outside the run-to-run spread).
+        self.direct_spec = os.environ.get("FP8GMM_EP_DIRECT", "auto")
         self._ptr_tables = {}
+        self._stage_out = None
+
+    def direct_homes(self):
+        """Home ranks whose rows the GEMM epilogues store directly (see __init__)."""
+        return direct_homes_for(self.direct_spec, self.rank, self.world)
+
+    def stage_out(self, nbytes):
+        """Local staging buffer for result rows that travel by copy (kept across steps: its address is part of the
+        epilogue's buffer table; a step's copies out of it are complete before the step's last wait returns)."""
+        if self._stage_out is None or self._stage_out.numel() < nbytes:
+            self._stage_out = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=self.device)
+            self._ptr_tables = {}
+        return self._stage_out
 
     def result_ptr_table(self, buf_ids):
-        """Device int64 vector: address, in this rank's address space, of rank r's result buffer buf_ids[r]."""
+        """Device int64 vector for the epilogue: address, in this rank's address space, of rank r's result buffer
+        buf_ids[r], and the local staging buffer as entry ``world``."""
         key = tuple(buf_ids)
         if key not in self._ptr_tables:
-            ptrs = [self.pool.buffers[b].ptrs[r] for r, b in enumerate(buf_ids)]
+            ptrs = [self.pool.buffers[b].ptrs[r] for r, b in enumerate(buf_ids)] + [self._stage_out.data_ptr()]
             self._ptr_tables[key] = torch.tensor(ptrs, dtype=torch.int64).to(self.device)
         return self._ptr_tables[key]
 
@@ -603,17 +656,18 @@ class _PeerEpMlp(torch.autograd.Function):
         pre_act = torch.empty(rows, fc1_out, dtype=torch.bfloat16, device=dev)
         act_fp8 = torch.empty(rows, ffn, dtype=fdt, device=dev)
         out = ectx.result_tensor(plan.out_ids[plan.rank], plan.rows_own, hidden)
-        direct = ectx.direct_combine
-        no_copies = np.empty(0, dtype=PeerChannel._BLOCK)
-        if direct:
-            # the fc2 epilogue stores every result row into its home rank's `out`: a combine round is only a signal
-            home_map, home_ptrs = plan.direct_row_map_dev(dev), ectx.result_ptr_table(plan.out_ids)
-            freed = False
+        # Results go home from the fc2 epilogue: rows of the home ranks in `homes` by stores into those ranks' `out`
+        # tensors, the others source-major into the staging buffer, from which one copy per (home rank, chunk) takes them
+        # (blocks of tens of MiB instead of one block per expert: the copy engines run faster on them).
+        homes = ectx.direct_homes()
+        out_np = np.asarray([ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+        stage_ptr = ectx.stage_out(rows * row_bytes).data_ptr()
+        if homes:
+            home_map, stage_copies = plan.combine_map_dev(dev, homes), plan.combine_map(homes)[1]
+            home_ptrs = ectx.result_ptr_table(plan.out_ids)
+            freed = all(h == plan.rank for h in homes)      # this rank's own tensor needs no announcement from anybody
         else:
-            # results are written source-major inside each chunk by the fc2 epilogue, so one copy per (home rank, chunk)
-            # takes them home (blocks of tens of MiB instead of one block per expert: the copy engines run faster on them)
-            out_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
-            out_np = np.asarray([ectx.pool.buffers[plan.out_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+            out_local = ectx.stage_out(rows * row_bytes)[:rows * row_bytes].view(torch.bfloat16).view(rows, hidden)
             stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
@@ -643,16 +697,15 @@ class _PeerEpMlp(torch.autograd.Function):
                     c=act_fp8[r0:r1], pre_gelu_out=pre_act[r0:r1],
                     c_scales=ms(_T.kInputGroup2, _M.kScale, j0), c_amaxes=ms(_T.kInputGroup2, _M.kAmax, j0),
                     backward=False, activation=activation)
-                if direct and not freed:
+                if homes and not freed:
                     ectx.wait_buffers_free(plan)
                     freed = True
                 backend.fp8_gmm(
                     act_fp8[r0:r1], fc2_w_fp8[j0:j1], sizes_cpu[j0:j1],
                     ms(_T.kInputGroup2, _M.kScaleInv, j0), ms(_T.kWeightGroup2, _M.kScaleInv, j0),
-                    c=None if direct else out_local[r0:r1], backward=False,
-                    c_row_map=home_map[r0:r1] if direct else stage_map[r0:r1], c_peers=home_ptrs if direct else None)
-            last = ch_back.push_arrays(no_copies if direct else
-                                       _copy_blocks(out_np, stage_copies[(j0, j1)], out_local.data_ptr(), row_bytes))
+                    c=None if homes else out_local[r0:r1], backward=False,
+                    c_row_map=home_map[r0:r1] if homes else stage_map[r0:r1], c_peers=home_ptrs if homes else None)
+            last = ch_back.push_arrays(_copy_blocks(out_np, stage_copies[(j0, j1)], stage_ptr, row_bytes))
         ch_back.wait(last)
         if grad_on:
             # reserved now so that every rank knows where to push gradients; returns to the pool with ctx if
@@ -722,18 +775,18 @@ class _PeerEpMlp(torch.autograd.Function):
         grad_fc2 = torch.empty(ctx.fc2_shape, dtype=torch.bfloat16, device=dev) if wgrad else None
         gi = ctx.gi
         ctx.gi = None
-        direct = ectx.direct_combine
-        no_copies = np.empty(0, dtype=PeerChannel._BLOCK)
-        gi_local = None
+        homes = ectx.direct_homes()
         if dgrad:
             assert min(plan.gi_ids) >= 0, "input.requires_grad must agree on all ranks"
-            if direct:
+            gi_np = np.asarray([ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+            stage_ptr = ectx.stage_out(rows * row_bytes).data_ptr()
+            if homes:
                 # the gradient buffers were reserved (and announced free) together with the forward results: the
                 # compute stream has waited for that announcement in forward
-                home_map, home_ptrs = plan.direct_row_map_dev(dev), ectx.result_ptr_table(plan.gi_ids)
+                home_map, stage_copies = plan.combine_map_dev(dev, homes), plan.combine_map(homes)[1]
+                home_ptrs = ectx.result_ptr_table(plan.gi_ids)
             else:
-                gi_local = torch.empty(rows, hidden, dtype=torch.bfloat16, device=dev)
-                gi_np = np.asarray([ectx.pool.buffers[plan.gi_ids[r]].ptrs[r] for r in range(plan.world)], dtype=np.uint64)
+                gi_local = ectx.stage_out(rows * row_bytes)[:rows * row_bytes].view(torch.bfloat16).view(rows, hidden)
                 stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
@@ -779,15 +832,14 @@ class _PeerEpMlp(torch.autograd.Function):
                 dpre_si = ms(_T.kGradOutputGroup2, _M.kScaleInv, j0)
                 if dgrad:
                     backend.fp8_gmm(grad_pre_fp8[r0:r1], fc1_w_t[j0:j1], sizes_cpu[j0:j1], dpre_si,
-                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=None if direct else gi_local[r0:r1],
-                                    backward=True, b_is_kn=ctx.kn, c_row_map=home_map[r0:r1] if direct else stage_map[r0:r1],
-                                    c_peers=home_ptrs if direct else None)
+                                    ms(_T.kForwardWeightGroup1, _M.kScaleInv, j0), c=None if homes else gi_local[r0:r1],
+                                    backward=True, b_is_kn=ctx.kn, c_row_map=home_map[r0:r1] if homes else stage_map[r0:r1],
+                                    c_peers=home_ptrs if homes else None)
             elif wgrad:
                 grad_fc1[j0:j1].zero_()
                 grad_fc2[j0:j1].zero_()
             if dgrad:
-                last = ch_back.push_arrays(no_copies if direct else
-                                           _copy_blocks(gi_np, stage_copies[(j0, j1)], gi_local.data_ptr(), row_bytes))
+                last = ch_back.push_arrays(_copy_blocks(gi_np, stage_copies[(j0, j1)], stage_ptr, row_bytes))
             else:
                 last = ch_back.push([])
             if live and need_t:

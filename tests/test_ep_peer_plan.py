@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from fp8_gmm_b200.backend import ROW_MAP_PEER_SHIFT
-from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds, resolve_result_buffers
+from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds, direct_homes_for, resolve_result_buffers
 
 
 def _counts(P, E, seed, zeros=True):
@@ -81,6 +81,29 @@ def test_dispatch_then_combine_is_the_identity(P, E, chunks):
             back3[home[q]][row[q]] = recv[o][q]
     for s in range(P):
         assert (back3[s] == x[s]).all()
+    # Mixed: some home ranks are served by epilogue stores, the rest through the staging buffer (named as buffer P in
+    # the entries) and one copy per (home rank, chunk).
+    for direct_homes in [(), (0,), tuple(range(0, P, 2)), tuple(range(P))]:
+        back4 = [np.full_like(x[s], -1) for s in range(P)]
+        for o in range(P):
+            entries, copies = plans[o].combine_map(direct_homes)
+            buf, row = entries >> ROW_MAP_PEER_SHIFT, entries & ((1 << ROW_MAP_PEER_SHIFT) - 1)
+            staged = np.full_like(recv[o], -1)
+            for q in range(entries.size):
+                if buf[q] == P:
+                    assert (staged[row[q]] == -1).all()
+                    staged[row[q]] = recv[o][q]
+                else:
+                    assert buf[q] in direct_homes
+                    back4[buf[q]][row[q]] = recv[o][q]
+            for chunk in plans[o].chunks:
+                homes, dst, src, n = copies[chunk]
+                assert not set(homes.tolist()) & set(direct_homes)
+                for s, d, a, k in zip(homes.tolist(), dst.tolist(), src.tolist(), n.tolist()):
+                    assert (staged[a:a + k] != -1).all() or k == 0
+                    back4[s][d:d + k] = staged[a:a + k]
+        for s in range(P):
+            assert (back4[s] == x[s]).all(), direct_homes
 
 
 def test_chunks_cover_the_local_experts_once():
@@ -116,3 +139,12 @@ def test_result_buffer_resolution_is_the_same_on_every_rank():
     assert resolved == [[0, 1], [2, 3], [3, 4], [1, -2]]
     assert resolve_result_buffers([[0, 1], [1, 0]], 2) == (0, [[0, 1], [1, 0]])
     assert resolve_result_buffers([[-1, -2]], 0) == (1, [[0, -2]])
+
+
+def test_home_ranks_served_by_epilogue_stores():
+    assert direct_homes_for("auto", 1, 2) == (0, 1)
+    assert direct_homes_for("auto", 5, 8) == ()
+    assert direct_homes_for("none", 3, 4) == ()
+    assert direct_homes_for("all", 3, 4) == (0, 1, 2, 3)
+    assert direct_homes_for("2", 7, 8) == (0, 1, 7)
+    assert direct_homes_for("9", 1, 4) == (0, 1, 2, 3)

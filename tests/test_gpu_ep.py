@@ -25,9 +25,10 @@ def _worker(rank, port, errq, transport):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         if transport.startswith("peer"):
-            # how results go home: stored by the GEMM epilogue into the home rank's tensor, or staged + copy engines
-            os.environ["FP8GMM_EP_COMBINE"] = "staged" if transport.endswith("staged") else "direct"
-            transport = transport.replace("-staged", "")
+            # how results go home: stored by the GEMM epilogue into the home rank's tensor (all rows, or only the
+            # rank's own with the other rank's rows staged and copied), or all staged and pushed by the copy engines
+            os.environ["FP8GMM_EP_DIRECT"] = "none" if transport.endswith("staged") else "0" if transport.endswith("mixed") else "all"
+            transport = transport.replace("-staged", "").replace("-mixed", "")
         dev = torch.device("cuda", rank)
         torch.cuda.set_device(dev)
         dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
@@ -112,13 +113,13 @@ def _worker(rank, port, errq, transport):
         raise
 
 
-@pytest.mark.parametrize("transport", ["nccl", "peer", "peer-bf16", "peer-staged", "peer-bf16-staged"])
+@pytest.mark.parametrize("transport", ["nccl", "peer", "peer-bf16", "peer-staged", "peer-mixed"])
 def test_expert_parallel_matches_single_gpu(cuda, transport):
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs 2 GPUs")
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
-    port = 29900 + os.getpid() % 90 + {"nccl": 0, "peer": 100, "peer-bf16": 200, "peer-staged": 300, "peer-bf16-staged": 400}[transport]
+    port = 29900 + os.getpid() % 90 + {"nccl": 0, "peer": 100, "peer-bf16": 200, "peer-staged": 300, "peer-mixed": 400}[transport]
     procs = [ctx.Process(target=_worker, args=(r, port, errq, transport)) for r in range(WORLD)]
     for p in procs:
         p.start()
