@@ -160,16 +160,19 @@ class PeerPlan:
             self._lists[key] = (row_map, copies)
         return self._lists[key]
 
-    def staged_dispatch(self):
-        """The same source-major-inside-the-chunk layout for the way in: a rank's rows for one owner and one chunk of
-        experts are one contiguous run at the source (rows are sorted by global expert), so with a source-major staging
-        buffer at the owner one copy per (owner, chunk) delivers them, and the owner brings them expert-major with a
-        local block permutation (fp8gmm_block_permute_rows).
+    def staged_dispatch(self, rounds=None):
+        """The same source-major layout for the way in.  A rank's rows for one owner and a run of that owner's experts
+        are one contiguous run at the source (rows are sorted by global expert), so with a source-major staging buffer
+        at the owner one copy per (owner, round) delivers them, and the owner brings them expert-major with a local
+        block permutation (fp8gmm_block_permute_rows), chunk by chunk.  ``rounds``: [(first expert, end expert)] of
+        the dispatch rounds, each covering whole chunks (default: one round per chunk); fewer rounds mean fewer and
+        larger copies.
 
-        Returns (copies, perms): ``copies[chunk]`` = four int64 arrays (owner, dst_row in the owner's staging buffer,
+        Returns (copies, perms): ``copies[round]`` = four int64 arrays (owner, dst_row in the owner's staging buffer,
         src_row here, rows), owners in the staggered order; ``perms[chunk]`` = three int64 arrays (staged start,
         expert-major start, rows) of this rank's blocks (local expert, source) of the chunk."""
-        key = "stage_in"
+        rounds = tuple(self.chunks) if rounds is None else tuple(tuple(g) for g in rounds)
+        key = ("stage_in", rounds)
         if key not in self._lists:
             El, r, P = self.experts_local, self.rank, self.world
             by_all = self.by_owner.numpy()           # (owner, El, src)
@@ -178,16 +181,20 @@ class PeerPlan:
             send_off = self.send_off[r].numpy()      # (E + 1,)
             order = np.asarray(self._peer_order(), dtype=np.int64)
             copies, perms = {}, {}
-            for (j0, j1) in self.chunks:
-                cnt_all = by_all[:, j0:j1, :]                                  # (owner, jc, src)
+            for (g0, g1) in rounds:
+                cnt_all = by_all[:, g0:g1, :]                                  # (owner, jc, src)
                 per_src = cnt_all.sum(1)                                       # (owner, src)
-                src_base = np.cumsum(per_src, 1) - per_src                     # rows of earlier sources in the chunk
-                dst_row = exp_off[order, j0] + src_base[order, r]
-                copies[(j0, j1)] = (order, dst_row, send_off[order * El + j0], per_src[order, r])
+                src_base = np.cumsum(per_src, 1) - per_src                     # rows of earlier sources in the round
+                dst_row = exp_off[order, g0] + src_base[order, r]
+                copies[(g0, g1)] = (order, dst_row, send_off[order * El + g0], per_src[order, r])
                 cnt = cnt_all[r]                                               # (jc, src) at this owner
-                staged = int(exp_off[r, j0]) + src_base[r][None, :] + (np.cumsum(cnt, 0) - cnt)
-                perms[(j0, j1)] = (np.ascontiguousarray(staged.reshape(-1)), np.ascontiguousarray(blk_off[j0:j1].reshape(-1)),
-                                   np.ascontiguousarray(cnt.reshape(-1)))
+                staged = int(exp_off[r, g0]) + src_base[r][None, :] + (np.cumsum(cnt, 0) - cnt)
+                inside = [c for c in self.chunks if g0 <= c[0] and c[1] <= g1]
+                assert sum(c[1] - c[0] for c in inside) == g1 - g0, "a dispatch round covers whole chunks"
+                for (j0, j1) in inside:
+                    perms[(j0, j1)] = (np.ascontiguousarray(staged[j0 - g0:j1 - g0].reshape(-1)),
+                                       np.ascontiguousarray(blk_off[j0:j1].reshape(-1)),
+                                       np.ascontiguousarray(cnt[j0 - g0:j1 - g0].reshape(-1)))
             self._lists[key] = (copies, perms)
         return self._lists[key]
 
@@ -320,6 +327,26 @@ def resolve_result_buffers(picks, buffers_before):
     return missing, resolved
 
 
+def dispatch_rounds_for(spec, chunks):
+    """Expert ranges [(first, end)] of the forward dispatch rounds for FP8GMM_EP_DISPATCH_ROUNDS = ``spec``: "chunks" (one
+    round per chunk), a comma-separated list of chunk counts per round ("2,4": the first two chunks travel together,
+    then the next four; the last round takes what is left), or "auto" (the first two chunks, then the rest)."""
+    chunks = list(chunks)
+    if spec == "chunks" or len(chunks) <= 2:
+        return chunks
+    counts = [2, len(chunks) - 2] if spec == "auto" else [int(v) for v in spec.split(",")]
+    out, i = [], 0
+    for n in counts:
+        if i >= len(chunks) or n <= 0:
+            continue
+        part = chunks[i:i + n]
+        out.append((part[0][0], part[-1][1]))
+        i += n
+    if i < len(chunks):
+        out.append((chunks[i][0], chunks[-1][1]))
+    return out
+
+
 def direct_homes_for(spec, rank, world):
     """Home ranks served by the GEMM epilogue's peer stores for FP8GMM_EP_DIRECT = ``spec``: "all", "none", "auto" (all
     in a group of two, none in larger groups) or a number k (this rank and the k ranks after it)."""
@@ -397,6 +424,10 @@ class EpContext:
         self.recv_stage = None   # forward FP8 dispatch: source-major staging (one copy per sender and chunk lands here)
         # FP8GMM_EP_DISPATCH=blocks keeps one copy per (owner, expert) straight into expert-major place in forward too
         self.merged_dispatch = os.environ.get("FP8GMM_EP_DISPATCH", "merged") != "blocks"
+        # Rounds of the merged forward dispatch (dispatch_rounds_for): the copy engines pay a fixed 15-20 us per copy
+        # and work through a rank's copies one after the other (8 MiB copies reach 290 GB/s, 32 MiB 540, 128 MiB 700),
+        # so the rows of several chunks travel as one copy per owner where the chunks can wait for it.
+        self.dispatch_rounds_spec = os.environ.get("FP8GMM_EP_DISPATCH_ROUNDS", "auto")
         self._amax_stage = None
         self._amax_view = None
         # How results go home.  The fc2 (forward) and fc1 data-gradient (backward) epilogues can store a row straight
@@ -615,22 +646,32 @@ class _PeerEpMlp(torch.autograd.Function):
         # block permutation (which is also the copy that keeps the rows for the fc1 weight gradient) puts them
         # expert-major.  16-64 MiB copies instead of one 8 MiB copy per (owner, expert).
         merged = fp8d and ectx.merged_dispatch
+        chunks = plan.chunks
+        # dispatch rounds: one per chunk, or -- merged -- fewer rounds that each carry the rows of several chunks
+        rounds = dispatch_rounds_for(ectx.dispatch_rounds_spec, chunks) if merged else chunks
+        round_of = [next(i for i, (g0, g1) in enumerate(rounds) if g0 <= j0 and j1 <= g1) for (j0, j1) in chunks]
         if merged:
             stage_np = np.asarray(ectx.recv_stage.ptrs, dtype=np.uint64)
-            in_copies, in_perms = plan.staged_dispatch()
+            in_copies, in_perms = plan.staged_dispatch(rounds)
 
-        def dispatch(chunk, first):
-            extra = _amax_blocks(ectx, plan, amax_part, chunk) if fp8d else None
-            blocks = (_copy_blocks(stage_np, in_copies[chunk], x_ptr, d_bytes, extra) if merged else
-                      _copy_blocks(recv_np, plan.dispatch_arrays(chunk), x_ptr, d_bytes, extra))
+        def dispatch(experts, first):
+            extra = _amax_blocks(ectx, plan, amax_part, experts) if fp8d else None
+            blocks = (_copy_blocks(stage_np, in_copies[experts], x_ptr, d_bytes, extra) if merged else
+                      _copy_blocks(recv_np, plan.dispatch_arrays(experts), x_ptr, d_bytes, extra))
             # later rounds do not wait for the compute stream: the rows they carry were ready before the first round
             return ch.push_arrays(blocks, after_compute=first)
 
         # The first rounds are queued now (the rows are ready), the rest as the chunks before them are reached, so
         # that the copy engines see dispatch and combine rounds interleaved (EpContext.dispatch_ahead).
-        chunks = plan.chunks
         ahead = max(1, ectx.dispatch_ahead)
-        seq = [dispatch(chunk, i == 0) for i, chunk in enumerate(chunks[:ahead])]
+        seq = []
+
+        def push_until(n):
+            while len(seq) < min(n, len(rounds)):
+                seq.append(dispatch(rounds[len(seq)], not seq))
+
+        push_until(ahead)
+        waited = -1
         # the fc2 weight cast runs while the first rows are on their way
         cache, reuse = st["weight_cache"], st["reuse_weights"]
         fc1_w_fp8, fc1_w_t = st["fc1_fp8"]   # cast before the size exchange, so the GPU had work during the host sync
@@ -671,9 +712,11 @@ class _PeerEpMlp(torch.autograd.Function):
             stage_map, stage_copies = plan.staged_row_map(dev), plan.staged_combine()[1]
         last = None
         for c, (j0, j1) in enumerate(chunks):
-            if c + ahead < len(chunks):
-                seq.append(dispatch(chunks[c + ahead], False))
-            ch.wait(seq[c])
+            u = round_of[c]
+            push_until(u + ahead + 1)
+            if u != waited:
+                ch.wait(seq[u])
+                waited = u
             r0, r1 = cumsums[j0], cumsums[j1]
             if fp8d:
                 _merge_amax(ectx, plan, ms(_T.kInputGroup1, _M.kAmax, j0), (j0, j1))

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from fp8_gmm_b200.backend import ROW_MAP_PEER_SHIFT
-from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds, direct_homes_for, resolve_result_buffers
+from fp8_gmm_b200.ep_peer import PeerPlan, chunk_bounds, direct_homes_for, dispatch_rounds_for, resolve_result_buffers
 
 
 def _counts(P, E, seed, zeros=True):
@@ -148,3 +148,51 @@ def test_home_ranks_served_by_epilogue_stores():
     assert direct_homes_for("all", 3, 4) == (0, 1, 2, 3)
     assert direct_homes_for("2", 7, 8) == (0, 1, 7)
     assert direct_homes_for("9", 1, 4) == (0, 1, 2, 3)
+
+
+@pytest.mark.parametrize("P,E,chunks,spec", [(2, 8, 4, "chunks"), (4, 16, 4, "auto"), (8, 32, "tapered", "auto"),
+                                             (4, 32, "tapered", "1,2,3"), (2, 12, 3, "2,2")])
+def test_merged_dispatch_rounds_then_block_permutation_is_the_expert_major_layout(P, E, chunks, spec):
+    """Forward dispatch through the source-major staging buffer: one copy per (owner, round), a round carrying the rows
+    of one or several chunks, then the owner's block permutation chunk by chunk -- must leave exactly what the
+    per-expert copies straight into expert-major place leave."""
+    counts = _counts(P, E, seed=P * 10 + E)
+    plans = [PeerPlan(counts, r, chunks) for r in range(P)]
+    x = []
+    for s in range(P):
+        expert = np.repeat(np.arange(E), counts[s].numpy())
+        x.append(np.stack([np.full(expert.shape, s), np.arange(expert.size), expert], 1))
+    want = [np.full((int(sum(plans[o].local_sizes)), 3), -1) for o in range(P)]
+    for s in range(P):
+        for chunk in plans[s].chunks:
+            for o, d, src, n in plans[s].dispatch_blocks(chunk):
+                want[o][d:d + n] = x[s][src:src + n]
+    rounds = dispatch_rounds_for(spec, plans[0].chunks)
+    assert rounds[0][0] == 0 and rounds[-1][1] == E // P and all(a[1] == b[0] for a, b in zip(rounds, rounds[1:]))
+    staging = [np.full_like(want[o], -1) for o in range(P)]
+    for s in range(P):
+        copies, _ = plans[s].staged_dispatch(rounds)
+        assert sorted(copies) == sorted(rounds)
+        for rnd in rounds:
+            owners, dst, src, n = copies[rnd]
+            assert sorted(owners.tolist()) == list(range(P)), "one copy per owner and round"
+            for o, d, a, k in zip(owners.tolist(), dst.tolist(), src.tolist(), n.tolist()):
+                assert (staging[o][d:d + k] == -1).all(), "two copies overlap in the staging buffer"
+                staging[o][d:d + k] = x[s][a:a + k]
+    for o in range(P):
+        got = np.full_like(want[o], -1)
+        _, perms = plans[o].staged_dispatch(rounds)
+        assert sorted(perms) == sorted(plans[o].chunks)
+        for chunk in plans[o].chunks:
+            for a, d, k in zip(*[v.tolist() for v in perms[chunk]]):
+                got[d:d + k] = staging[o][a:a + k]
+        assert (got == want[o]).all()
+
+
+def test_dispatch_round_specs():
+    chunks = chunk_bounds(16, "tapered")
+    assert dispatch_rounds_for("chunks", chunks) == chunks
+    assert dispatch_rounds_for("auto", chunks) == [(0, 3), (3, 16)]
+    assert dispatch_rounds_for("1,2,3", chunks) == [(0, 1), (1, 7), (7, 16)]
+    assert dispatch_rounds_for("2,2", chunks) == [(0, 3), (3, 11), (11, 16)]     # the last round takes what is left
+    assert dispatch_rounds_for("auto", chunk_bounds(4, 2)) == [(0, 2), (2, 4)]   # two chunks: nothing to merge

@@ -29,6 +29,8 @@ def _worker(rank, port, errq, transport):
             # rank's own with the other rank's rows staged and copied), or all staged and pushed by the copy engines
             os.environ["FP8GMM_EP_DIRECT"] = "none" if transport.endswith("staged") else "0" if transport.endswith("mixed") else "all"
             transport = transport.replace("-staged", "").replace("-mixed", "")
+        # four chunks of one expert: the merged forward dispatch then sends two chunks per round (FP8 dispatch only)
+        chunks = 4 if transport == "peer" else 2
         dev = torch.device("cuda", rank)
         torch.cuda.set_device(dev)
         dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
@@ -46,7 +48,7 @@ def _worker(rank, port, errq, transport):
             dys.append(torch.randn(n, H, generator=gr).to(torch.bfloat16))
         El = E // WORLD
         model = ep.ExpertParallelMlp(H, F, E, torch.bfloat16, device=dev, activation="swiglu",
-                                     transport=transport.split("-")[0], num_chunks=2,
+                                     transport=transport.split("-")[0], num_chunks=chunks,
                                      fp8_dispatch=not transport.endswith("bf16"))
         with torch.no_grad():
             model.mlp.fc1_weight.copy_(w1[rank * El:(rank + 1) * El])
