@@ -150,7 +150,7 @@ def test_home_ranks_served_by_epilogue_stores():
     assert direct_homes_for("9", 1, 4) == (0, 1, 2, 3)
 
 
-@pytest.mark.parametrize("P,E,chunks,spec", [(2, 8, 4, "chunks"), (4, 16, 4, "auto"), (8, 32, "tapered", "auto"),
+@pytest.mark.parametrize("P,E,chunks,spec", [(2, 8, 4, "chunks"), (4, 16, 4, "2,2"), (8, 32, "tapered", "2,4"),
                                              (4, 32, "tapered", "1,2,3"), (2, 12, 3, "2,2")])
 def test_merged_dispatch_rounds_then_block_permutation_is_the_expert_major_layout(P, E, chunks, spec):
     """Forward dispatch through the source-major staging buffer: one copy per (owner, round), a round carrying the rows
@@ -192,7 +192,8 @@ def test_merged_dispatch_rounds_then_block_permutation_is_the_expert_major_layou
 def test_dispatch_round_specs():
     chunks = chunk_bounds(16, "tapered")
     assert dispatch_rounds_for("chunks", chunks) == chunks
-    assert dispatch_rounds_for("auto", chunks) == [(0, 3), (3, 16)]
+    assert dispatch_rounds_for("auto", chunks) == chunks
+    assert dispatch_rounds_for("2,4", chunks) == [(0, 3), (3, 16)]
     assert dispatch_rounds_for("1,2,3", chunks) == [(0, 1), (1, 7), (7, 16)]
     assert dispatch_rounds_for("2,2", chunks) == [(0, 3), (3, 11), (11, 16)]     # the last round takes what is left
-    assert dispatch_rounds_for("auto", chunk_bounds(4, 2)) == [(0, 2), (2, 4)]   # two chunks: nothing to merge
+    assert dispatch_rounds_for("2,4", chunk_bounds(4, 2)) == [(0, 2), (2, 4)]    # two chunks: nothing to merge

@@ -29,8 +29,9 @@ def _worker(rank, port, errq, transport):
             # rank's own with the other rank's rows staged and copied), or all staged and pushed by the copy engines
             os.environ["FP8GMM_EP_DIRECT"] = "none" if transport.endswith("staged") else "0" if transport.endswith("mixed") else "all"
             transport = transport.replace("-staged", "").replace("-mixed", "")
-        # four chunks of one expert: the merged forward dispatch then sends two chunks per round (FP8 dispatch only)
+        # four chunks of one expert, the merged forward dispatch sending two chunks per round (FP8 dispatch only)
         chunks = 4 if transport == "peer" else 2
+        os.environ["FP8GMM_EP_DISPATCH_ROUNDS"] = "2,2"
         dev = torch.device("cuda", rank)
         torch.cuda.set_device(dev)
         dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
