@@ -74,14 +74,26 @@ def even_sizes(groups, rows):
     return sizes
 
 
-def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label, b_is_kn=False):
-    """b_is_kn: B is (G, K, N) and read MN-major (how dgrad consumes the forward weights by default)."""
+def gemm_case(backend, dev, sizes, n, k, act, a_dtype, iters, warmup, label, b_is_kn=False, buffers=0):
+    """b_is_kn: B is (G, K, N) and read MN-major (how dgrad consumes the forward weights by default).
+    buffers > 0: the epilogue stores its rows into that many result buffers named by a row map (the expert-parallel
+    combine; here all buffers are in this GPU's memory): runs of 1000 rows go to the buffers in turn."""
     G, m = len(sizes), sum(sizes)
     a = rand_fp8((m, k), a_dtype, dev, 1)
     b = rand_fp8((G, k, n) if b_is_kn else (G, n, k), E4, dev, 2)
     ones = torch.ones(G, device=dev)
     ms_sizes = torch.tensor(sizes)
-    if act == "none":
+    if act == "none" and buffers > 0:
+        rows = torch.arange(m, dtype=torch.int64)
+        run = rows // 1000
+        buf = run % buffers
+        row_in_buf = (run // buffers) * 1000 + rows % 1000
+        entries = backend.peer_row_entry(buf, row_in_buf).to(torch.int32).to(dev)
+        outs = [torch.empty(int(row_in_buf[buf == r].max()) + 1, n, dtype=torch.bfloat16, device=dev) for r in range(buffers)]
+        table = torch.tensor([t.data_ptr() for t in outs], dtype=torch.int64).to(dev)
+        fn = lambda: backend.fp8_gmm(a, b, ms_sizes, ones, ones, c_row_map=entries, c_peers=table, b_is_kn=b_is_kn)  # noqa: E731
+        label += f", rows stored into {buffers} buffers through the row map"
+    elif act == "none":
         c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: backend.fp8_gmm(a, b, ms_sizes, ones, ones, c=c, b_is_kn=b_is_kn)  # noqa: E731
     else:
@@ -282,6 +294,7 @@ def main():
     p.add_argument("--k", type=int, default=4096)
     p.add_argument("--act", default="none", choices=["none", "gelu", "swiglu"])
     p.add_argument("--a-format", default="e4m3", choices=["e4m3", "e5m2"])
+    p.add_argument("--buffers", type=int, default=0, help="gemm: store the rows into this many buffers through a row map")
     p.add_argument("--max-rows", type=int, default=4096)
     p.add_argument("--cols", type=int, default=7168)
     p.add_argument("--mode", default="cast", choices=PAD_MODES)
@@ -298,7 +311,7 @@ def main():
     if args.what == "gemm":
         sizes = even_sizes(args.groups or 8, args.rows)
         print(json.dumps(gemm_case(backend, dev, sizes, args.n, args.k, args.act, E4 if args.a_format == "e4m3" else E5,
-                                   args.iters, args.warmup, "custom")))
+                                   args.iters, args.warmup, "custom", buffers=args.buffers)))
     elif args.what == "scaled-mm":
         sizes = even_sizes(args.groups or 8, args.rows)
         print(json.dumps(scaled_mm_case(dev, sizes, args.n, args.k, args.iters, args.warmup, "custom")))
