@@ -440,7 +440,8 @@ class EpContext:
         # k (this rank and the k ranks after it) or "auto": all in a group of two, where the rows of one GEMM cross the
         # link faster than the GEMM computes them (17.1 against 18.4 ms per step); none in larger groups, where 3/4 and
         # more of the rows leave (4 GPUs, one box: all 21.1 ms per step against 19.0 staged; own rows only 18.5-19.8,
-        # own + next rank 18.5, none 18.8-18.9: no gain outside the run-to-run spread).
+        # own + next rank 18.5, none 18.8-18.9: no gain outside the run-to-run spread; 8 GPUs: none 19.9, own + next rank
+        # 20.9, own + next two 20.6 -- the waits shrink but the epilogues stall on the link for longer than that).
         self.direct_spec = os.environ.get("FP8GMM_EP_DIRECT", "auto")
         self._ptr_tables = {}
         self._stage_out = None
